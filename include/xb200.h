@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XB_ABI_VERSION 3
+#define XB_ABI_VERSION 4
 
 typedef struct xb_engine xb_engine;
 
@@ -203,6 +203,60 @@ int xb_reserve_sms(xb_engine* e, int n);
  * tokens_out: device int32 [n]. */
 int xb_sample(xb_engine* e, const float* logits, int n, float temp, int top_k, float top_p, const float* q,
               uint64_t seed, int32_t* tokens_out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Hybrid models: a decoder whose layers are described one by one (no counterpart in the reference,
+ * whose models are all Llama-shaped, general_mha.py:23-176).  Each layer has one token mixer and an
+ * optional feed-forward; the residual stream, the norms and every recurrent state are fp32.  A hybrid
+ * engine is a full model (first and last shard in one) and is driven through the same calls as any
+ * other engine: xb_kv_reserve (slots = KV pages of the attention layers + recurrent state + filter
+ * tails), xb_forward / xb_forward_rows, xb_kv_release_slot, xb_sample, xb_load_safetensors.
+ * A sequence that starts at position 0 finds empty state whatever its slot held before. */
+enum {
+  XB_MIX_DELTA = 1,    /* gated delta rule: short causal filter + SiLU on q/k/v, unit-length q/k, per-head decay
+                          exp(-exp(A_log) softplus(a + dt_bias)), write strength sigmoid(b), read-out RMS-normed per head
+                          and gated by SiLU(g) */
+  XB_MIX_PARALLEL = 2  /* two mixers on the same input, summed with left_scale / right_scale:
+                          left = grouped-query softmax attention without rotation, causal window + kept first tokens,
+                                 q/k/v bias, sigmoid output gate;
+                          right = HGRN2 (forget gate f = lower + (1 - lower) sigmoid(.), input gate 1 - f), read-out
+                                 RMS-normed per head */
+};
+
+typedef struct xb_hybrid_layer {
+  int32_t mixer;                                    /* XB_MIX_* */
+  int32_t ff;                                       /* width of the squared-ReLU feed-forward, 0 = none */
+  int32_t d_heads, d_kv_heads, d_dim, d_vdim, d_taps;                 /* XB_MIX_DELTA */
+  int32_t a_heads, a_kv_heads, a_dim, a_vdim, a_window, a_keep_first; /* XB_MIX_PARALLEL, left */
+  float a_scale;                                                      /* score = q.k * a_scale */
+  int32_t r_heads, r_dim, r_vdim;                                     /* XB_MIX_PARALLEL, right */
+  float left_scale, right_scale;
+} xb_hybrid_layer;
+
+typedef struct xb_hybrid_desc {
+  uint32_t struct_size, layer_size;  /* sizeof(xb_hybrid_desc), sizeof(xb_hybrid_layer) of the caller's header */
+  int32_t n_layers, dim, vocab;
+  int32_t taps;                      /* causal filter on what every sublayer reads (h + filter(h)); 0 = none */
+  int32_t side_dim;                  /* per-layer token side input of this width after each layer; 0 = none */
+  float norm_eps;
+  float logit_softcap;               /* logits <- cap * tanh(logits / cap); 0 = none */
+  int32_t compute_fp32;              /* 0: Linears read bf16 activations (serving); 1: everything in fp32, plain FMA */
+  int32_t max_batch_tokens, max_seqs;
+  int32_t max_logit_rows;            /* most rows one xb_forward_rows call may ask logits for */
+} xb_hybrid_desc;
+
+int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybrid_layer* layers, int device, xb_engine** out);
+
+/* One tensor of a hybrid model by its checkpoint name ("embed", "l3.mix.q.conv", "l1.mix.left.q.b", ...), from host
+ * or device memory.  dtype: 0 bf16, 1 fp16, 2 fp32.  xb_load_safetensors feeds a hybrid engine through the same
+ * name table; xb_weights_missing lists what is still absent. */
+int xb_load_named(xb_engine* e, const char* name, const void* src, int dtype, const int64_t* shape, int ndim);
+
+/* xb_forward that returns the logits of chosen token rows instead of each sequence's last one: rows (host, n_rows
+ * indices into the batch's token rows, any order) -> out fp32 [n_rows, vocab].  n_rows == 0 runs the step for its
+ * effect on the cache and state only.  taps (hybrid engines): fp32 [T, dim] per layer.  Hybrid engines only. */
+int xb_forward_rows(xb_engine* e, const xb_batch* batch, const int32_t* rows, int n_rows, void* out, void* const* taps,
+                    void* stream);
 
 int xb_get_counters(xb_engine* e, xb_counters* out);
 

@@ -13,6 +13,7 @@ SYMBOLS = (
   "xb_load_safetensors", "xb_weights_missing", "xb_safetensors_list",
   "xb_kv_reserve", "xb_kv_release_slot", "xb_kv_slot_len", "xb_forward", "xb_forward_host_logits", "xb_sample",
   "xb_handoff_create", "xb_handoff_connect", "xb_forward_handoff", "xb_handoff_connect_local", "xb_handoff_clear_error", "xb_reserve_sms",
+  "xb_engine_create_hybrid", "xb_load_named", "xb_forward_rows",
   "xb_get_counters", "xb_debug_linear", "xb_bench_linears", "xb_bench_attention", "xb_linear_noalloc", "xb_debug_timeline",
 )
 
@@ -36,12 +37,41 @@ class ModelDesc(C.Structure):
   ]
 
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 def model_desc(**fields) -> ModelDesc:
   """ModelDesc with ``struct_size`` set: xb_engine_create rejects a descriptor laid out by another header."""
   return ModelDesc(struct_size=C.sizeof(ModelDesc), **fields)
+
+
+MIX_DELTA, MIX_PARALLEL = 1, 2
+ST_BF16, ST_F16, ST_F32 = 0, 1, 2   # element types xb_load_named accepts
+
+
+class HybridLayer(C.Structure):
+  """xb_hybrid_layer: one layer of a hybrid model -- its token mixer and the width of its feed-forward."""
+  _fields_ = [
+    ("mixer", C.c_int32), ("ff", C.c_int32),
+    ("d_heads", C.c_int32), ("d_kv_heads", C.c_int32), ("d_dim", C.c_int32), ("d_vdim", C.c_int32), ("d_taps", C.c_int32),
+    ("a_heads", C.c_int32), ("a_kv_heads", C.c_int32), ("a_dim", C.c_int32), ("a_vdim", C.c_int32),
+    ("a_window", C.c_int32), ("a_keep_first", C.c_int32), ("a_scale", C.c_float),
+    ("r_heads", C.c_int32), ("r_dim", C.c_int32), ("r_vdim", C.c_int32),
+    ("left_scale", C.c_float), ("right_scale", C.c_float),
+  ]
+
+
+class HybridDesc(C.Structure):
+  _fields_ = [
+    ("struct_size", C.c_uint32), ("layer_size", C.c_uint32),
+    ("n_layers", C.c_int32), ("dim", C.c_int32), ("vocab", C.c_int32), ("taps", C.c_int32), ("side_dim", C.c_int32),
+    ("norm_eps", C.c_float), ("logit_softcap", C.c_float), ("compute_fp32", C.c_int32),
+    ("max_batch_tokens", C.c_int32), ("max_seqs", C.c_int32), ("max_logit_rows", C.c_int32),
+  ]
+
+
+def hybrid_desc(**fields) -> HybridDesc:
+  return HybridDesc(struct_size=C.sizeof(HybridDesc), layer_size=C.sizeof(HybridLayer), **fields)
 
 
 class Batch(C.Structure):
@@ -98,6 +128,10 @@ def load():
   lib.xb_forward_handoff.argtypes = [C.c_void_p, C.POINTER(Batch), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
   lib.xb_sample.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_uint64,
                             C.c_void_p, C.c_void_p]
+  lib.xb_engine_create_hybrid.argtypes = [C.POINTER(HybridDesc), C.POINTER(HybridLayer), C.c_int, C.POINTER(C.c_void_p)]
+  lib.xb_load_named.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int, C.POINTER(C.c_int64), C.c_int]
+  lib.xb_forward_rows.argtypes = [C.c_void_p, C.POINTER(Batch), C.POINTER(C.c_int32), C.c_int, C.c_void_p, C.POINTER(C.c_void_p),
+                                  C.c_void_p]
   lib.xb_get_counters.argtypes = [C.c_void_p, C.POINTER(Counters)]
   lib.xb_debug_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                   C.c_int, C.c_int, C.c_void_p]

@@ -37,6 +37,15 @@ struct LayerW {
 
 enum Site { SITE_QKV = 0, SITE_O, SITE_GU, SITE_DOWN, SITE_HEAD };
 
+struct xb_engine;
+struct HyModel;
+static void hy_destroy(HyModel* hy);
+static int hy_reserve(xb_engine* e);
+static int hy_missing(xb_engine* e, char* buf, size_t buflen, int* n_missing);
+static int hy_load_file(xb_engine* e, const char* path, const std::vector<StEntry>& entries, const uint8_t* data, size_t data_size,
+                        int* n_tensors, uint64_t* n_bytes);
+// hybrid models (xb_hybrid.cuh): per-layer mixers, fp32 residual, recurrent state in the slots
+
 struct xb_engine {
   xb_model_desc d;
   int device = 0;
@@ -107,6 +116,9 @@ struct xb_engine {
   xb_counters c{};
   std::map<long long, int> loaded;   // (layer + 1) * 64 + kind -> seen by xb_load_weight / xb_load_safetensors
   StRing* ring = nullptr;            // loader staging, alive from the first file until the shard is complete
+  HyModel* hy = nullptr;             // non-null: a hybrid model; e->d then carries only the fields the bookkeeping reads
+  const int32_t* sel_rows = nullptr; // xb_forward_rows: logits of these token rows (host) instead of each sequence's last
+  int sel_n = 0;
 };
 
 #define LAUNCH_COUNT(e) ((e)->c.launches++)
@@ -197,6 +209,34 @@ static int store_tiled(bf16* dst, const void* src, size_t row0, size_t rows, siz
   XB_CUDA(cudaGetLastError());
   XB_CUDA(cudaDeviceSynchronize());
   if (staging) cudaFree(staging);
+  return 0;
+}
+
+// Device + pinned host blocks of the per-forward metadata (token -> sequence, positions, slots, prefill tiles, the
+// compact decode block); e->d.max_batch_tokens / max_seqs and e->tile_tokens must be set.
+static int alloc_batch_meta(xb_engine* e) {
+  const xb_model_desc& d = e->d;
+  const size_t T = d.max_batch_tokens;
+  e->max_tiles = (int)(T / e->tile_tokens) + d.max_seqs + 1;
+  e->meta_ints = 2 * T + 2 * (size_t)d.max_seqs + 2 * (size_t)e->max_tiles + 4;
+  XB_TRY(dmalloc((void**)&e->d_meta, e->meta_ints * 4));
+  e->d_tok_seq = e->d_meta;
+  e->d_tok_pos = e->d_meta + T;
+  e->d_seq_slot = e->d_meta + 2 * T;
+  e->d_seq_last = e->d_meta + 2 * T + d.max_seqs;
+  e->d_tile_start = e->d_meta + 2 * T + 2 * d.max_seqs;
+  e->d_tile_len = e->d_tile_start + e->max_tiles;
+  {
+    XB_TRY(dmalloc((void**)&e->d_dec, (4 + 4 * XB_DEC_ROWS) * 4));
+    int ident[4 + 4 * XB_DEC_ROWS] = {0};
+    for (int i = 0; i < XB_DEC_ROWS; ++i) ident[4 + 2 * XB_DEC_ROWS + i] = ident[4 + 3 * XB_DEC_ROWS + i] = i;
+    XB_CUDA(cudaMemcpy(e->d_dec, ident, sizeof(ident), cudaMemcpyHostToDevice));
+  }
+  e->d_ctl = reinterpret_cast<HandoffCtl*>(e->d_dec);   // the peer hand-off carries decode steps only
+  for (int i = 0; i < xb_engine::META_RING; ++i) {
+    XB_CUDA(cudaMallocHost((void**)&e->h_meta_ring[i], (e->meta_ints + 4 + 2 * XB_DEC_ROWS) * 4));
+    XB_CUDA(cudaEventCreateWithFlags(&e->meta_ev[i], cudaEventDisableTiming));
+  }
   return 0;
 }
 
@@ -297,26 +337,7 @@ extern "C" int xb_engine_create(const xb_model_desc* desc, int device, xb_engine
   XB_TRY(dmalloc((void**)&e->o_part, Tsplit * d.n_heads * e->max_attn_splits * d.head_dim * sizeof(float)));
   XB_TRY(dmalloc((void**)&e->ml_part, Tsplit * d.n_heads * e->max_attn_splits * 2 * sizeof(float)));
   e->tile_tokens = 128 / (d.n_heads / d.n_kv_heads);
-  e->max_tiles = (int)(T / e->tile_tokens) + d.max_seqs + 1;
-  e->meta_ints = 2 * T + 2 * (size_t)d.max_seqs + 2 * (size_t)e->max_tiles + 4;
-  XB_TRY(dmalloc((void**)&e->d_meta, e->meta_ints * 4));
-  e->d_tok_seq = e->d_meta;
-  e->d_tok_pos = e->d_meta + T;
-  e->d_seq_slot = e->d_meta + 2 * T;
-  e->d_seq_last = e->d_meta + 2 * T + d.max_seqs;
-  e->d_tile_start = e->d_meta + 2 * T + 2 * d.max_seqs;
-  e->d_tile_len = e->d_tile_start + e->max_tiles;
-  {
-    XB_TRY(dmalloc((void**)&e->d_dec, (4 + 4 * XB_DEC_ROWS) * 4));
-    int ident[4 + 4 * XB_DEC_ROWS] = {0};
-    for (int i = 0; i < XB_DEC_ROWS; ++i) ident[4 + 2 * XB_DEC_ROWS + i] = ident[4 + 3 * XB_DEC_ROWS + i] = i;
-    XB_CUDA(cudaMemcpy(e->d_dec, ident, sizeof(ident), cudaMemcpyHostToDevice));
-  }
-  e->d_ctl = reinterpret_cast<HandoffCtl*>(e->d_dec);   // the peer hand-off carries decode steps only
-  for (int i = 0; i < xb_engine::META_RING; ++i) {
-    XB_CUDA(cudaMallocHost((void**)&e->h_meta_ring[i], (e->meta_ints + 4 + 2 * XB_DEC_ROWS) * 4));
-    XB_CUDA(cudaEventCreateWithFlags(&e->meta_ev[i], cudaEventDisableTiming));
-  }
+  XB_TRY(alloc_batch_meta(e));
   XB_TRY(dmalloc((void**)&e->in_tokens, T * 4));
   if (last) XB_TRY(dmalloc((void**)&e->logits, (size_t)d.max_seqs * d.vocab * sizeof(float)));
   {
@@ -349,6 +370,8 @@ extern "C" int xb_engine_destroy(xb_engine* e) {
   }
   cudaSetDevice(e->device);
   cudaDeviceSynchronize();
+  hy_destroy(e->hy);
+  e->hy = nullptr;
   for (LayerW& w : e->L) {
     cudaFree(w.wqkv); cudaFree(w.bqkv); cudaFree(w.wo); cudaFree(w.wgu); cudaFree(w.wdown);
     cudaFree(w.sa_norm); cudaFree(w.mlp_norm); cudaFree(w.k_pool); cudaFree(w.v_pool);
@@ -431,6 +454,7 @@ static int resolve_target(xb_engine* e, int layer, int kind, WTarget* t) {
 
 extern "C" int xb_load_weight(xb_engine* e, int layer, int kind, const void* src, size_t nbytes) {
   XB_CHECK(e != nullptr && src != nullptr, "null argument");
+  XB_CHECK(e->hy == nullptr, "a hybrid engine takes its tensors by name (xb_load_named)");
   XB_CUDA(cudaSetDevice(e->device));
   WTarget t;
   XB_TRY(resolve_target(e, layer, kind, &t));
@@ -505,6 +529,7 @@ extern "C" int xb_load_safetensors(xb_engine* e, const char* path, int permute_q
   XB_CHECK(st_parse_header((const char*)f.base + 8, (size_t)hlen, &entries), "%s: cannot parse the safetensors header", path);
   const uint8_t* data = f.base + 8 + hlen;
   const size_t data_size = f.size - 8 - (size_t)hlen;
+  if (e->hy != nullptr) return hy_load_file(e, path, entries, data, data_size, n_tensors, n_bytes);
   int rc = 0;
   if (e->ring == nullptr) {
     e->ring = new StRing();
@@ -621,6 +646,7 @@ extern "C" int xb_safetensors_list(const char* path, char* buf, size_t buflen, i
 // Names (ABI kinds) this shard still lacks; 0 in *n_missing = ready.  `buf` receives a readable list.
 extern "C" int xb_weights_missing(xb_engine* e, char* buf, size_t buflen, int* n_missing) {
   XB_CHECK(e != nullptr && n_missing != nullptr, "null argument");
+  if (e->hy != nullptr) return hy_missing(e, buf, buflen, n_missing);
   static const char* names[] = {"q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "input_layernorm",
                                 "post_attention_layernorm", "q_proj.bias", "k_proj.bias", "v_proj.bias", "embed_tokens",
                                 "final norm", "lm_head", "rope table"};
@@ -675,6 +701,7 @@ extern "C" int xb_kv_reserve(xb_engine* e, int n_slots, int max_tokens_per_slot,
   e->n_pages = n_slots * e->max_pages;
   const size_t pool_bytes = (size_t)e->n_pages * e->NKV * page_tokens * 2;
   const long long pool_rows = (long long)e->n_pages * e->d.n_kv_heads * page_tokens;
+  if (e->hy != nullptr) XB_TRY(hy_reserve(e));   // pools of the attention layers + the slots' recurrent state and filter tails
   for (LayerW& w : e->L) {
     if (w.wqkv == nullptr) continue;   // boundary layer whose attention block runs on the previous stage: no cache here
     XB_TRY(dmalloc((void**)&w.k_pool, pool_bytes));
@@ -922,8 +949,11 @@ static void fill_batch_meta(const xb_engine* e, BatchMeta& m) {
   }
 }
 
+#include "xb_hybrid.cuh"
+
 static int run_body(xb_engine* e, int T, int n_seqs, int n_splits, int n_tiles, void* const* taps, cudaStream_t st,
                     int ho_in = 0, int ho_out = 0, int with_head = 1) {
+  if (e->hy != nullptr) return hy_run_body(e, T, n_seqs, taps, st, with_head);
   const xb_model_desc& d = e->d;
   const bool first = shard_is_first(d), last = shard_is_last(d);
   BatchMeta m;
@@ -1158,15 +1188,17 @@ static int forward_impl(xb_engine* e, const xb_batch* b, void* out, void* const*
   // decode: split every context across blocks (split-KV); prefill: one block per (query tile,
   // kv head), no kv split
   int n_splits = 1;
-  if (decode_only) {
+  if (decode_only && e->hy == nullptr) {
     n_splits = choose_kv_splits(e, T, max_ctx);   // 1 once T * kv heads exceeds one wave (no split workspace needed)
   }
 
-  if (decode_only && e->use_graphs && taps == nullptr && st != nullptr && st != cudaStreamLegacy) {
+  if (e->sel_rows != nullptr && e->sel_n > 0)
+    XB_CUDA(cudaMemcpyAsync(hy_rows_buffer(e), e->sel_rows, (size_t)e->sel_n * 4, cudaMemcpyHostToDevice, st));
+  if (decode_only && e->use_graphs && taps == nullptr && e->sel_rows == nullptr && st != nullptr && st != cudaStreamLegacy) {
     // decode step: replay a captured graph (first call of a shape runs eagerly to build the
     // launch plans and set kernel attributes, second call captures)
     // host_logits: the head runs after the graph (its host pointer changes from call to call)
-    const int headless = host_logits != nullptr && last;
+    const int headless = host_logits != nullptr && last && e->hy == nullptr;
     const long long key = ((long long)b->n_seqs << 16) | (n_splits << 3) | (headless << 2) | (ho_in << 1) | ho_out;
     xb_engine::StepGraph& sg = e->graphs[key];
     if (sg.exec == nullptr && sg.warmed) {
@@ -1191,15 +1223,18 @@ static int forward_impl(xb_engine* e, const xb_batch* b, void* out, void* const*
     }
     if (headless) XB_TRY(run_head(e, b->n_seqs, st, host_logits));
   } else {
-    const int headless = host_logits != nullptr && last;
+    const int headless = host_logits != nullptr && last && e->hy == nullptr;
     XB_TRY(run_body(e, T, b->n_seqs, n_splits, n_tiles, taps, st, ho_in, ho_out, !headless));
     if (headless) XB_TRY(run_head(e, b->n_seqs, st, host_logits));
   }
 
   if (out != nullptr && !(ho_out && !last)) {
-    if (last) XB_CUDA(cudaMemcpyAsync(out, e->logits, (size_t)b->n_seqs * d.vocab * sizeof(float), cudaMemcpyDeviceToDevice, st));
-    else XB_CUDA(cudaMemcpyAsync(out, e->h, (size_t)T * d.dim * 2, cudaMemcpyDeviceToDevice, st));
+    const size_t n_out = e->sel_rows != nullptr ? (size_t)e->sel_n : (size_t)b->n_seqs;
+    if (!last) XB_CUDA(cudaMemcpyAsync(out, e->h, (size_t)T * d.dim * 2, cudaMemcpyDeviceToDevice, st));
+    else if (n_out > 0) XB_CUDA(cudaMemcpyAsync(out, e->logits, n_out * d.vocab * sizeof(float), cudaMemcpyDeviceToDevice, st));
   }
+  if (host_logits != nullptr && e->hy != nullptr)   // hybrid head: the logits reach the caller's pinned buffer by a copy behind the step
+    XB_CUDA(cudaMemcpyAsync(host_logits, e->logits, (size_t)b->n_seqs * d.vocab * sizeof(float), cudaMemcpyDefault, st));
   e->c.forwards++;
   return 0;
 }
@@ -1208,9 +1243,88 @@ extern "C" int xb_forward(xb_engine* e, const xb_batch* b, void* out, void* cons
   return forward_impl(e, b, out, taps, stream, nullptr);
 }
 
+extern "C" int xb_forward_rows(xb_engine* e, const xb_batch* b, const int32_t* rows, int n_rows, void* out, void* const* taps,
+                               void* stream) {
+  XB_CHECK(e != nullptr && b != nullptr && (rows != nullptr || n_rows == 0), "null argument");
+  XB_CHECK(e->hy != nullptr, "xb_forward_rows serves hybrid engines");
+  int T = 0;
+  for (int i = 0; i < b->n_seqs; ++i) T += b->q_lens[i];
+  XB_CHECK(n_rows >= 0 && n_rows <= hy_max_rows(e), "%d logit rows asked, the engine was created for %d", n_rows, hy_max_rows(e));
+  for (int i = 0; i < n_rows; ++i) XB_CHECK(rows[i] >= 0 && rows[i] < T, "row %d is outside the batch's %d token rows", rows[i], T);
+  static const int32_t none = 0;
+  e->sel_rows = n_rows > 0 ? rows : &none;
+  e->sel_n = n_rows;
+  const int rc = forward_impl(e, b, out, taps, stream, nullptr);
+  e->sel_rows = nullptr;
+  e->sel_n = 0;
+  return rc;
+}
+
+extern "C" int xb_load_named(xb_engine* e, const char* name, const void* src, int dtype, const int64_t* shape, int ndim) {
+  XB_CHECK(e != nullptr && name != nullptr && src != nullptr && shape != nullptr && ndim >= 1 && ndim <= 2, "bad argument");
+  XB_CHECK(e->hy != nullptr, "xb_load_named serves hybrid engines");
+  XB_CUDA(cudaSetDevice(e->device));
+  cudaPointerAttributes pa;
+  const bool on_device = cudaPointerGetAttributes(&pa, src) == cudaSuccess && pa.type == cudaMemoryTypeDevice;
+  cudaGetLastError();
+  long long sh[2] = {shape[0], ndim > 1 ? shape[1] : 1};
+  return hy_store(e, name, src, dtype, sh, ndim, on_device);
+}
+
+extern "C" int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybrid_layer* layers, int device, xb_engine** out) {
+  XB_CHECK(desc != nullptr && layers != nullptr && out != nullptr, "null argument");
+  int ndev = 0;
+  cudaError_t ce = cudaGetDeviceCount(&ndev);
+  XB_CHECK(ce == cudaSuccess && ndev > 0, "no CUDA device available (%s): libxb200 has no CPU fallback", cudaGetErrorString(ce));
+  XB_CHECK(device >= 0 && device < ndev, "device %d out of range (%d devices)", device, ndev);
+  XB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  XB_CUDA(cudaGetDeviceProperties(&prop, device));
+  XB_CHECK(prop.major == 10, "libxb200 is built for sm_100a only; device %d is sm_%d%d", device, prop.major, prop.minor);
+  XB_CHECK(desc->struct_size == sizeof(xb_hybrid_desc) && desc->layer_size == sizeof(xb_hybrid_layer),
+           "xb_hybrid_desc / xb_hybrid_layer sizes %u / %u differ from this library's %zu / %zu: the caller was built against another xb200.h",
+           desc->struct_size, desc->layer_size, sizeof(xb_hybrid_desc), sizeof(xb_hybrid_layer));
+  const xb_hybrid_desc& h = *desc;
+  XB_CHECK(h.n_layers > 0 && h.dim > 0 && h.vocab > 0, "n_layers, dim and vocab must be > 0");
+  XB_CHECK(h.dim <= 12288, "dim %d: the row kernels keep a row in 48 KB of shared memory (<= 12288)", h.dim);
+  XB_CHECK(h.taps >= 0 && h.taps <= HY_MAX_TAPS && h.side_dim >= 0, "bad taps %d (0..%d) / side_dim %d", h.taps, HY_MAX_TAPS, h.side_dim);
+  XB_CHECK(h.max_batch_tokens > 0 && h.max_seqs > 0 && h.max_logit_rows >= 0, "max_batch_tokens / max_seqs must be > 0");
+  xb_engine* e = new xb_engine();
+  // the fields of the Llama-shaped description that the shared bookkeeping reads
+  e->d = xb_model_desc{};
+  e->d.struct_size = sizeof(xb_model_desc);
+  e->d.n_layers = h.n_layers;
+  e->d.start_layer = 0;
+  e->d.end_layer = h.n_layers - 1;
+  e->d.dim = h.dim;
+  e->d.vocab = h.vocab;
+  e->d.norm_eps = h.norm_eps;
+  e->d.max_positions = 1 << 30;   // no rotation table bounds the positions
+  e->d.max_batch_tokens = h.max_batch_tokens;
+  e->d.max_seqs = h.max_seqs;
+  e->device = device;
+  e->num_sms = prop.multiProcessorCount;
+  e->nl = 0;
+  e->tile_tokens = 128;
+  int rc = alloc_batch_meta(e);
+  if (rc == 0) rc = dmalloc((void**)&e->in_tokens, (size_t)h.max_batch_tokens * 4);
+  if (rc == 0) rc = hy_create(e, h, layers);
+  if (rc != 0) {
+    const std::string msg = g_xb_err;
+    xb_engine_destroy(e);
+    g_xb_err = msg;
+    return rc;
+  }
+  const char* g = getenv("XB_GRAPHS");
+  if (g != nullptr && g[0] == '0') e->use_graphs = 0;
+  *out = e;
+  return 0;
+}
+
 extern "C" int xb_forward_host_logits(xb_engine* e, const xb_batch* b, void* out, float* host_logits, void* stream) {
   XB_CHECK(e != nullptr && host_logits != nullptr, "null argument");
   XB_CHECK(shard_is_last(e->d), "xb_forward_host_logits needs a last shard (it produces logits)");
+  XB_CHECK(e->hy == nullptr || b == nullptr || b->n_seqs <= e->d.max_seqs, "too many sequences");
   cudaPointerAttributes pa;
   XB_CHECK(cudaPointerGetAttributes(&pa, host_logits) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer != nullptr,
            "host_logits must be page-locked host memory the device can address (cudaHostAlloc / torch pin_memory)");
@@ -1321,6 +1435,7 @@ extern "C" int xb_handoff_connect(xb_engine* e, const void* next_landing_handle,
 // back to back on `stream`, on the engine's own weights and workspaces.  The caller brackets
 // the call with CUDA events; the launch count is returned in *n_launches.
 extern "C" int xb_bench_linears(xb_engine* e, int T, int iters, int* n_launches, void* stream) {
+  XB_CHECK(e != nullptr && e->hy == nullptr, "this measurement hook serves Llama-shaped engines");
   XB_CHECK(e != nullptr && T > 0 && T <= e->d.max_batch_tokens && iters > 0, "bad argument");
   const xb_model_desc& d = e->d;
   cudaStream_t st = (cudaStream_t)stream;
@@ -1375,6 +1490,7 @@ extern "C" int xb_bench_linears(xb_engine* e, int T, int iters, int* n_launches,
 // count (0 = the engine's own choice for that batch).  The caller brackets it with CUDA events.
 extern "C" int xb_bench_attention(xb_engine* e, int n_seqs, int max_ctx, int n_splits, int iters, int* splits_used,
                                   void* stream) {
+  XB_CHECK(e != nullptr && e->hy == nullptr, "this measurement hook serves Llama-shaped engines");
   XB_CHECK(e != nullptr && n_seqs > 0 && n_seqs <= e->d.max_seqs && iters > 0, "bad argument");
   const xb_model_desc& d = e->d;
   cudaStream_t st = (cudaStream_t)stream;

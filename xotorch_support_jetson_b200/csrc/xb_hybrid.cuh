@@ -1,0 +1,483 @@
+// Host side of hybrid models (xb_hybrid_desc / xb_hybrid_layer in xb200.h): weights by checkpoint name, per-slot
+// state (recurrent matrices + filter tails) beside the paged KV pools, and the launch sequence of one forward.
+// Included by xb_engine.cu after the definition of xb_engine: batch bookkeeping, page lists, metadata upload,
+// CUDA-graph replay of decode steps, sampling and the loader are the engine's own.
+#pragma once
+#include "xb_hybrid_kernels.cuh"
+#include <set>
+
+struct HyTarget {
+  void* dst = nullptr;
+  bool f32 = false;          // destination type: fp32 (vectors, filters) or bf16 (matrices, tables)
+  long long rows = 0, cols = 0, ld = 0;
+  int ndim = 0;
+};
+
+struct HyLayer {
+  xb_hybrid_layer d{};
+  int n_in = 0;              // rows of the fused input projection
+  int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_b = 0, off_a = 0, off_rq = 0, off_rf = 0, off_rv = 0;
+  int c_conv = 0;            // delta: channels that pass the short filter (q | k | v)
+  int n_o = 0, n_o2 = 0;     // inputs of the output projection(s)
+  bf16 *w_in = nullptr, *w_o = nullptr, *w_o2 = nullptr, *w_up = nullptr, *w_down = nullptr, *w_sgate = nullptr, *w_sproj = nullptr;
+  float *b_in = nullptr, *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *canon1 = nullptr,
+        *canon2 = nullptr, *side_norm = nullptr, *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr, *head_norm = nullptr,
+        *lower = nullptr;
+  void *k_pool = nullptr, *v_pool = nullptr;
+  size_t st_rec = 0, st_conv = 0, st_canon1 = 0, st_canon2 = 0;   // float offsets inside a slot's state
+};
+
+struct HyModel {
+  xb_hybrid_desc d{};
+  std::vector<HyLayer> L;
+  bf16 *embed = nullptr, *side_embed = nullptr, *head = nullptr;
+  float* final_norm = nullptr;
+  float* state = nullptr;
+  size_t state_floats = 0;   // per slot
+  float *x = nullptr, *hn = nullptr, *P = nullptr, *c = nullptr, *o = nullptr, *m1 = nullptr, *m2 = nullptr, *beta = nullptr,
+        *decay = nullptr, *head_raw = nullptr;
+  void *a1 = nullptr, *a2 = nullptr, *head_in = nullptr;
+  int* d_rows = nullptr;
+  size_t maxN = 0, maxK = 0, maxC = 0, maxO = 0, maxH = 1;
+  std::map<std::string, HyTarget> names;
+  std::set<std::string> loaded;
+  std::vector<void*> allocs;
+};
+
+static int* hy_rows_buffer(xb_engine* e) { return e->hy->d_rows; }
+static int hy_max_rows(xb_engine* e) { return e->hy->d.max_logit_rows > e->hy->d.max_seqs ? e->hy->d.max_logit_rows : e->hy->d.max_seqs; }
+
+static int hy_alloc(HyModel* hy, void** p, size_t bytes) {
+  XB_TRY(dmalloc(p, bytes));
+  XB_CUDA(cudaMemset(*p, 0, bytes ? bytes : 16));
+  hy->allocs.push_back(*p);
+  return 0;
+}
+template <typename T>
+static int hy_alloc_t(HyModel* hy, T** p, size_t n) { return hy_alloc(hy, (void**)p, n * sizeof(T)); }
+
+static void hy_name(HyModel* hy, const std::string& name, void* dst, bool f32, long long rows, long long cols, long long ld, int ndim) {
+  HyTarget t;
+  t.dst = dst; t.f32 = f32; t.rows = rows; t.cols = cols; t.ld = ld; t.ndim = ndim;
+  hy->names[name] = t;
+}
+// a matrix that occupies rows [row0, row0 + rows) of a fused bf16 matrix with K columns
+static void hy_name_rows(HyModel* hy, const std::string& name, bf16* base, long long row0, long long rows, long long K) {
+  hy_name(hy, name, base + row0 * K, false, rows, K, K, 2);
+}
+static void hy_name_vec(HyModel* hy, const std::string& name, float* dst, long long n) { hy_name(hy, name, dst, true, 1, n, n, 1); }
+
+static void hy_destroy(HyModel* hy) {
+  if (hy == nullptr) return;
+  for (void* p : hy->allocs) cudaFree(p);
+  for (HyLayer& l : hy->L) { cudaFree(l.k_pool); cudaFree(l.v_pool); }
+  cudaFree(hy->state);
+  delete hy;
+}
+
+static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_layer* layers) {
+  HyModel* hy = new HyModel();
+  e->hy = hy;
+  hy->d = d;
+  hy->L.resize(d.n_layers);
+  const size_t D = d.dim, Tm = d.max_batch_tokens;
+  const int ct = d.taps;
+  size_t st = 0;
+  uint64_t wbytes = 0, kvpos = 0;
+  hy->maxN = D; hy->maxK = D; hy->maxC = 1; hy->maxO = 1;
+  if (d.side_dim > 0) { if ((size_t)d.side_dim > hy->maxN) hy->maxN = d.side_dim; if ((size_t)d.side_dim > hy->maxK) hy->maxK = d.side_dim; }
+  for (int i = 0; i < d.n_layers; ++i) {
+    HyLayer& l = hy->L[i];
+    l.d = layers[i];
+    const xb_hybrid_layer& c = l.d;
+    const std::string p = "l" + std::to_string(i) + ".";
+    XB_TRY(hy_alloc_t(hy, &l.norm1, D)); hy_name_vec(hy, p + "norm1", l.norm1, D);
+    XB_TRY(hy_alloc_t(hy, &l.norm1b, D)); hy_name_vec(hy, p + "norm1b", l.norm1b, D);
+    if (ct > 0) {
+      XB_TRY(hy_alloc_t(hy, &l.canon1, D * ct)); hy_name(hy, p + "canon1", l.canon1, true, D, ct, ct, 2);
+      l.st_canon1 = st; st += (size_t)(ct - 1) * D;
+    }
+    if (c.mixer == XB_MIX_DELTA) {
+      const long long H = c.d_heads, G = c.d_kv_heads, dk = c.d_dim, dv = c.d_vdim, tp = c.d_taps;
+      XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 32 * HY_MAX_KREG && dv > 0, "layer %d: bad delta-rule sizes (key dim <= %d)", i, 32 * HY_MAX_KREG);
+      XB_CHECK(tp >= 1 && tp <= HY_MAX_TAPS, "layer %d: short filter of %lld taps (1..%d)", i, tp, HY_MAX_TAPS);
+      l.off_q = 0; l.off_k = (int)(G * dk); l.off_v = (int)(2 * G * dk);
+      l.c_conv = (int)(2 * G * dk + H * dv);
+      l.off_g = l.c_conv; l.off_b = l.off_g + (int)(H * dv); l.off_a = l.off_b + (int)H;
+      l.n_in = l.off_a + (int)H;
+      l.n_o = (int)(H * dv);
+      XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+      XB_TRY(hy_alloc_t(hy, &l.b_in, (size_t)l.n_in));
+      XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
+      XB_TRY(hy_alloc_t(hy, &l.conv_w, (size_t)l.c_conv * tp));
+      XB_TRY(hy_alloc_t(hy, &l.A_log, (size_t)H));
+      XB_TRY(hy_alloc_t(hy, &l.dt_bias, (size_t)H));
+      XB_TRY(hy_alloc_t(hy, &l.head_norm, (size_t)dv));
+      hy_name_rows(hy, p + "mix.q", l.w_in, l.off_q, G * dk, D);
+      hy_name_rows(hy, p + "mix.k", l.w_in, l.off_k, G * dk, D);
+      hy_name_rows(hy, p + "mix.v", l.w_in, l.off_v, H * dv, D);
+      hy_name_rows(hy, p + "mix.g", l.w_in, l.off_g, H * dv, D);
+      hy_name_rows(hy, p + "mix.b", l.w_in, l.off_b, H, D);
+      hy_name_rows(hy, p + "mix.a", l.w_in, l.off_a, H, D);
+      hy_name(hy, p + "mix.q.conv", l.conv_w + (size_t)l.off_q * tp, true, G * dk, tp, tp, 2);
+      hy_name(hy, p + "mix.k.conv", l.conv_w + (size_t)l.off_k * tp, true, G * dk, tp, tp, 2);
+      hy_name(hy, p + "mix.v.conv", l.conv_w + (size_t)l.off_v * tp, true, H * dv, tp, tp, 2);
+      hy_name_vec(hy, p + "mix.A_log", l.A_log, H);
+      hy_name_vec(hy, p + "mix.dt_bias", l.dt_bias, H);
+      hy_name_vec(hy, p + "mix.norm", l.head_norm, dv);
+      hy_name_rows(hy, p + "mix.o", l.w_o, 0, D, l.n_o);
+      l.st_rec = st; st += (size_t)(H * dv * dk);
+      if ((size_t)H > hy->maxH) hy->maxH = H;
+      l.st_conv = st; st += (size_t)(tp - 1) * l.c_conv;
+      if ((size_t)l.c_conv > hy->maxC) hy->maxC = l.c_conv;
+      if ((size_t)l.n_o > hy->maxO) hy->maxO = l.n_o;
+      wbytes += ((size_t)l.n_in * D + D * l.n_o) * 2;
+    } else if (c.mixer == XB_MIX_PARALLEL) {
+      const long long H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
+      const long long Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
+      XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 256, "layer %d: bad attention sizes (value dim <= 256)", i);
+      XB_CHECK(c.a_window >= 1 && c.a_keep_first >= 0, "layer %d: bad window %d / kept first tokens %d", i, c.a_window, c.a_keep_first);
+      XB_CHECK(Hr > 0 && rk > 0 && rk <= 32 * HY_MAX_KREG && rv > 0, "layer %d: bad HGRN2 sizes (key dim <= %d)", i, 32 * HY_MAX_KREG);
+      l.off_q = 0; l.off_k = (int)(H * dk); l.off_v = l.off_k + (int)(G * dk); l.off_g = l.off_v + (int)(G * dv);
+      l.off_rq = l.off_g + (int)(H * dv); l.off_rf = l.off_rq + (int)(Hr * rk); l.off_rv = l.off_rf + (int)(Hr * rk);
+      l.n_in = l.off_rv + (int)(Hr * rv);
+      l.n_o = (int)(H * dv); l.n_o2 = (int)(Hr * rv);
+      XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+      XB_TRY(hy_alloc_t(hy, &l.b_in, (size_t)l.n_in));
+      XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
+      XB_TRY(hy_alloc_t(hy, &l.w_o2, D * l.n_o2));
+      XB_TRY(hy_alloc_t(hy, &l.lower, (size_t)(Hr * rk)));
+      XB_TRY(hy_alloc_t(hy, &l.head_norm, (size_t)rv));
+      hy_name_rows(hy, p + "mix.left.q", l.w_in, l.off_q, H * dk, D);   hy_name_vec(hy, p + "mix.left.q.b", l.b_in + l.off_q, H * dk);
+      hy_name_rows(hy, p + "mix.left.k", l.w_in, l.off_k, G * dk, D);   hy_name_vec(hy, p + "mix.left.k.b", l.b_in + l.off_k, G * dk);
+      hy_name_rows(hy, p + "mix.left.v", l.w_in, l.off_v, G * dv, D);   hy_name_vec(hy, p + "mix.left.v.b", l.b_in + l.off_v, G * dv);
+      hy_name_rows(hy, p + "mix.left.g", l.w_in, l.off_g, H * dv, D);
+      hy_name_rows(hy, p + "mix.left.o", l.w_o, 0, D, l.n_o);
+      hy_name_rows(hy, p + "mix.right.q", l.w_in, l.off_rq, Hr * rk, D);
+      hy_name_rows(hy, p + "mix.right.f", l.w_in, l.off_rf, Hr * rk, D); hy_name_vec(hy, p + "mix.right.f.b", l.b_in + l.off_rf, Hr * rk);
+      hy_name_rows(hy, p + "mix.right.v", l.w_in, l.off_rv, Hr * rv, D);
+      hy_name_vec(hy, p + "mix.right.lower", l.lower, Hr * rk);
+      hy_name_vec(hy, p + "mix.right.norm", l.head_norm, rv);
+      hy_name_rows(hy, p + "mix.right.o", l.w_o2, 0, D, l.n_o2);
+      l.st_rec = st; st += (size_t)(Hr * rv * rk);
+      const size_t cc = (size_t)(2 * Hr * rk + Hr * rv);
+      if (cc > hy->maxC) hy->maxC = cc;
+      if ((size_t)l.n_o > hy->maxO) hy->maxO = l.n_o;
+      if ((size_t)l.n_o2 > hy->maxO) hy->maxO = l.n_o2;
+      wbytes += ((size_t)l.n_in * D + D * l.n_o + D * l.n_o2) * 2;
+      kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
+    } else {
+      return xb_fail(1, "layer %d: unknown mixer kind %d", i, c.mixer);
+    }
+    if ((size_t)l.n_in > hy->maxN) hy->maxN = l.n_in;
+    if ((size_t)l.n_o > hy->maxK) hy->maxK = l.n_o;
+    if ((size_t)l.n_o2 > hy->maxK) hy->maxK = l.n_o2;
+    if (c.ff > 0) {
+      const size_t F = c.ff;
+      XB_TRY(hy_alloc_t(hy, &l.norm2, D)); hy_name_vec(hy, p + "norm2", l.norm2, D);
+      XB_TRY(hy_alloc_t(hy, &l.norm2b, D)); hy_name_vec(hy, p + "norm2b", l.norm2b, D);
+      XB_TRY(hy_alloc_t(hy, &l.w_up, F * D)); hy_name_rows(hy, p + "mlp.up", l.w_up, 0, F, D);
+      XB_TRY(hy_alloc_t(hy, &l.w_down, D * F)); hy_name_rows(hy, p + "mlp.down", l.w_down, 0, D, F);
+      if (ct > 0) {
+        XB_TRY(hy_alloc_t(hy, &l.canon2, D * ct)); hy_name(hy, p + "canon2", l.canon2, true, D, ct, ct, 2);
+        l.st_canon2 = st; st += (size_t)(ct - 1) * D;
+      }
+      if (F > hy->maxN) hy->maxN = F;
+      if (F > hy->maxK) hy->maxK = F;
+      wbytes += 2 * F * D * 2;
+    }
+    if (d.side_dim > 0) {
+      const size_t sd = d.side_dim;
+      XB_TRY(hy_alloc_t(hy, &l.w_sgate, sd * D)); hy_name_rows(hy, p + "side.gate", l.w_sgate, 0, sd, D);
+      XB_TRY(hy_alloc_t(hy, &l.w_sproj, D * sd)); hy_name_rows(hy, p + "side.proj", l.w_sproj, 0, D, sd);
+      XB_TRY(hy_alloc_t(hy, &l.side_norm, D)); hy_name_vec(hy, p + "side.norm", l.side_norm, D);
+      wbytes += 2 * sd * D * 2;
+    }
+  }
+  hy->state_floats = st;
+  XB_TRY(hy_alloc_t(hy, &hy->embed, (size_t)d.vocab * D)); hy_name_rows(hy, "embed", hy->embed, 0, d.vocab, D);
+  XB_TRY(hy_alloc_t(hy, &hy->head, (size_t)d.vocab * D)); hy_name_rows(hy, "head", hy->head, 0, d.vocab, D);
+  XB_TRY(hy_alloc_t(hy, &hy->final_norm, D)); hy_name_vec(hy, "final.norm", hy->final_norm, D);
+  if (d.side_dim > 0) {
+    const size_t w = (size_t)d.side_dim * d.n_layers;
+    XB_TRY(hy_alloc_t(hy, &hy->side_embed, (size_t)d.vocab * w)); hy_name_rows(hy, "side.embed", hy->side_embed, 0, d.vocab, w);
+  }
+  wbytes += (size_t)d.vocab * D * 2;
+  const size_t as = d.compute_fp32 ? 4 : 2;
+  const size_t R = (size_t)(d.max_logit_rows > d.max_seqs ? d.max_logit_rows : d.max_seqs);
+  XB_TRY(hy_alloc_t(hy, &hy->x, Tm * D));
+  XB_TRY(hy_alloc_t(hy, &hy->hn, Tm * D));
+  XB_TRY(hy_alloc_t(hy, &hy->P, Tm * hy->maxN));
+  XB_TRY(hy_alloc_t(hy, &hy->c, Tm * hy->maxC));
+  XB_TRY(hy_alloc_t(hy, &hy->o, Tm * hy->maxO));
+  XB_TRY(hy_alloc_t(hy, &hy->m1, Tm * D));
+  XB_TRY(hy_alloc_t(hy, &hy->m2, Tm * D));
+  XB_TRY(hy_alloc_t(hy, &hy->beta, Tm * hy->maxH));
+  XB_TRY(hy_alloc_t(hy, &hy->decay, Tm * hy->maxH));
+  XB_TRY(hy_alloc(hy, &hy->a1, Tm * hy->maxK * as));
+  XB_TRY(hy_alloc(hy, &hy->a2, Tm * hy->maxK * as));
+  XB_TRY(hy_alloc(hy, &hy->head_in, R * D * as));
+  XB_TRY(hy_alloc_t(hy, &hy->head_raw, R * (size_t)d.vocab));
+  XB_TRY(hy_alloc_t(hy, &hy->d_rows, R));
+  XB_TRY(dmalloc((void**)&e->logits, R * (size_t)d.vocab * sizeof(float)));
+  e->c.weight_bytes = wbytes;
+  e->c.kv_bytes_per_pos = kvpos;
+  return 0;
+}
+
+// ----------------------------------------------------------------------------- weights
+static int hy_store(xb_engine* e, const std::string& name, const void* src, int dt, const long long* shape, int ndim, bool src_on_device) {
+  HyModel* hy = e->hy;
+  auto it = hy->names.find(name);
+  if (it == hy->names.end()) return xb_fail(1, "tensor %s is not part of this model", name.c_str());
+  const HyTarget& t = it->second;
+  XB_CHECK(dt >= 0 && dt <= 2, "tensor %s: unsupported element type", name.c_str());
+  long long numel = 1;
+  for (int i = 0; i < ndim; ++i) numel *= shape[i];
+  bool ok = numel == t.rows * t.cols && ndim == t.ndim;
+  if (ok && ndim == 2) ok = shape[0] == t.rows && shape[1] == t.cols;
+  if (!ok) {
+    std::string got;
+    for (int i = 0; i < ndim; ++i) got += (i ? "x" : "") + std::to_string(shape[i]);
+    return xb_fail(1, "tensor %s has shape %s, this model wants %lldx%lld", name.c_str(), got.c_str(), t.rows, t.cols);
+  }
+  const size_t bytes = (size_t)numel * (dt == 2 ? 4 : 2);
+  const void* dsrc = src;
+  void* staging = nullptr;
+  if (!src_on_device) {
+    XB_TRY(dmalloc(&staging, bytes));
+    XB_CUDA(cudaMemcpy(staging, src, bytes, cudaMemcpyHostToDevice));
+    dsrc = staging;
+  }
+  const unsigned blocks = (unsigned)((numel + 255) / 256);
+  if (t.f32) hy_load_convert_kernel<float><<<blocks, 256>>>(dsrc, dt, t.rows, t.cols, (float*)t.dst, t.ld);
+  else hy_load_convert_kernel<bf16><<<blocks, 256>>>(dsrc, dt, t.rows, t.cols, (bf16*)t.dst, t.ld);
+  XB_CUDA(cudaGetLastError());
+  XB_CUDA(cudaDeviceSynchronize());
+  if (staging) cudaFree(staging);
+  hy->loaded.insert(name);
+  return 0;
+}
+
+static int hy_load_file(xb_engine* e, const char* path, const std::vector<StEntry>& entries, const uint8_t* data, size_t data_size,
+                        int* n_tensors, uint64_t* n_bytes) {
+  int count = 0;
+  uint64_t total = 0;
+  for (const StEntry& en : entries) {
+    if (e->hy->names.find(en.name) == e->hy->names.end()) continue;
+    const int dt = st_dtype_code(en.dtype);
+    XB_CHECK(dt >= 0, "%s: tensor %s has unsupported dtype %s (BF16, F16, F32)", path, en.name.c_str(), en.dtype.c_str());
+    long long numel = 1;
+    for (long long v : en.shape) numel *= v;
+    XB_CHECK(en.end <= data_size && en.end - en.begin == (size_t)numel * st_dtype_size(dt), "%s: tensor %s: size and shape disagree",
+             path, en.name.c_str());
+    XB_TRY(hy_store(e, en.name, data + en.begin, dt, en.shape.data(), (int)en.shape.size(), false));
+    ++count;
+    total += en.end - en.begin;
+  }
+  if (n_tensors) *n_tensors = count;
+  if (n_bytes) *n_bytes = total;
+  return 0;
+}
+
+static int hy_missing(xb_engine* e, char* buf, size_t buflen, int* n_missing) {
+  std::string out;
+  int n = 0;
+  for (const auto& kv : e->hy->names) {
+    if (e->hy->loaded.count(kv.first)) continue;
+    ++n;
+    if (out.size() < 900) out += kv.first + "; ";
+  }
+  *n_missing = n;
+  if (buf != nullptr && buflen > 0) {
+    strncpy(buf, out.c_str(), buflen - 1);
+    buf[buflen - 1] = 0;
+  }
+  return 0;
+}
+
+// ----------------------------------------------------------------------------- slots: KV pools + state
+static int hy_reserve(xb_engine* e) {
+  HyModel* hy = e->hy;
+  const size_t es = hy->d.compute_fp32 ? 4 : 2;
+  for (HyLayer& l : hy->L) {
+    cudaFree(l.k_pool); cudaFree(l.v_pool);
+    l.k_pool = l.v_pool = nullptr;
+    if (l.d.mixer != XB_MIX_PARALLEL) continue;
+    const size_t kb = (size_t)e->n_pages * l.d.a_kv_heads * e->page_tokens * l.d.a_dim * es;
+    const size_t vb = (size_t)e->n_pages * l.d.a_kv_heads * e->page_tokens * l.d.a_vdim * es;
+    XB_TRY(dmalloc(&l.k_pool, kb));
+    XB_TRY(dmalloc(&l.v_pool, vb));
+    XB_CUDA(cudaMemset(l.k_pool, 0, kb));
+    XB_CUDA(cudaMemset(l.v_pool, 0, vb));
+  }
+  cudaFree(hy->state);
+  hy->state = nullptr;
+  const size_t sb = (size_t)e->n_slots * (hy->state_floats ? hy->state_floats : 1) * sizeof(float);
+  XB_TRY(dmalloc((void**)&hy->state, sb));
+  XB_CUDA(cudaMemset(hy->state, 0, sb));
+  return 0;
+}
+
+// ----------------------------------------------------------------------------- forward
+template <typename... KArgs, typename... Args>
+static int hy_launch(xb_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  XB_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+  e->c.launches++;
+  return 0;
+}
+
+static LinOut hy_plain(const float* f, long long ld) {
+  LinOut o;
+  o.f = f; o.h = nullptr; o.si = SplitInfo{0, 0, 0}; o.plane = 0; o.ld = ld;
+  return o;
+}
+static LinOut hy_none() { return hy_plain(nullptr, 0); }
+
+// y[T, N] = x[T, K] w^T + bias into `out` (fp32, row pitch N)
+template <typename AT>
+static int hy_linear(xb_engine* e, const void* x, long long ldx, const bf16* w, const float* bias, int T, int N, int K, float* out,
+                     cudaStream_t st, LinOut* y) {
+  const AT* xa = reinterpret_cast<const AT*>(x);
+  if (T <= HY_SMALL_T)
+    XB_TRY(hy_launch(e, hy_linear_small_kernel<AT>, dim3((N + 7) / 8), dim3(256), 0, st, xa, ldx, w, bias, out, (long long)N, T, N, K));
+  else
+    XB_TRY(hy_launch(e, hy_linear_tiled_kernel<AT>, dim3((N + 63) / 64, (T + 63) / 64), dim3(256), 0, st, xa, ldx, w, bias, out,
+                     (long long)N, T, N, K));
+  *y = hy_plain(out, N);
+  return 0;
+}
+
+template <typename AT>
+static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float s2, const float* bw, float bw_one, const float* nw,
+                     void* xa, cudaStream_t st) {
+  HyModel* hy = e->hy;
+  RowOpArgs a;
+  a.x = hy->x; a.m1 = m1; a.m2 = m2; a.s1 = s1; a.s2 = s2; a.bw = bw; a.bw_one = bw_one; a.nw = nw; a.hn = hy->hn; a.xa = xa;
+  a.eps = hy->d.norm_eps; a.D = hy->d.dim;
+  return hy_launch(e, hy_row_op_kernel<AT, 256>, dim3(T), dim3(256), (size_t)hy->d.dim * sizeof(float), st, a);
+}
+
+// what a sublayer reads: the normed stream plus its causal filter, as a Linear input; then the slot's new tail
+template <typename AT>
+static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, const float* w, size_t st_off, const BatchMeta& m, cudaStream_t st) {
+  HyModel* hy = e->hy;
+  const int D = hy->d.dim, taps = hy->d.taps;
+  const LinOut in = hy_plain(hy->hn, D);
+  float* tail = hy->state + st_off;
+  XB_TRY(hy_launch(e, hy_taps_kernel<AT>, dim3(T, (D + 255) / 256), dim3(256), 0, st, in, 0, D, taps, w, (const float*)tail,
+                   (long long)hy->state_floats, m, 1, 0, reinterpret_cast<AT*>(hy->a1), (long long)D));
+  if (taps > 1)
+    XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (D + 255) / 256), dim3(256), 0, st, in, 0, D, taps, tail,
+                     (long long)hy->state_floats, m));
+  return 0;
+}
+
+template <typename AT>
+static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cudaStream_t st, int with_head) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_desc& d = hy->d;
+  typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
+  BatchMeta m;
+  fill_batch_meta(e, m);
+  m.page_table = e->d_page_table;
+  m.tile_start = e->d_tile_start;
+  m.tile_len = e->d_tile_len;
+  m.max_pages = e->max_pages;
+  m.page_tokens = e->page_tokens;
+  const int D = d.dim;
+  const long long SS = (long long)hy->state_floats;
+  AT* a1 = reinterpret_cast<AT*>(hy->a1);
+  AT* a2 = reinterpret_cast<AT*>(hy->a2);
+  XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab));
+  XB_TRY(hy_row_op<AT>(e, T, hy_none(), 0.f, hy_none(), 0.f, nullptr, 0.f, hy->L[0].norm1, nullptr, st));
+  for (int li = 0; li < d.n_layers; ++li) {
+    const HyLayer& l = hy->L[li];
+    const xb_hybrid_layer& c = l.d;
+    const float* next_norm = li + 1 < d.n_layers ? hy->L[li + 1].norm1 : hy->final_norm;
+    const bool has_ff = c.ff > 0, has_side = d.side_dim > 0;
+    LinOut P, y1, y2 = hy_none();
+    float s1 = 1.f, s2 = 0.f;
+    XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, l.canon1, l.st_canon1, m, st));
+    XB_TRY(hy_linear<AT>(e, a1, D, l.w_in, l.b_in, T, l.n_in, D, hy->P, st, &P));
+    if (c.mixer == XB_MIX_DELTA) {
+      const int H = c.d_heads, G = c.d_kv_heads, dk = c.d_dim, dv = c.d_vdim, tp = c.d_taps;
+      float* tail = hy->state + l.st_conv;
+      XB_TRY(hy_launch(e, hy_taps_kernel<float>, dim3(T, (l.c_conv + 255) / 256), dim3(256), 0, st, P, 0, l.c_conv, tp,
+                       (const float*)l.conv_w, (const float*)tail, SS, m, 0, 1, hy->c, (long long)l.c_conv));
+      if (tp > 1)
+        XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (l.c_conv + 255) / 256), dim3(256), 0, st, P, 0, l.c_conv, tp, tail, SS, m));
+      XB_TRY(hy_launch(e, hy_delta_prep_kernel, dim3(T), dim3(256), 0, st, hy->c, (long long)l.c_conv, P, l.off_b, l.off_a,
+                       (const float*)l.A_log, (const float*)l.dt_bias, hy->beta, hy->decay, H, G, dk));
+      XB_TRY(hy_launch(e, hy_delta_rule_kernel, dim3(n_seqs, H, (dv + 7) / 8), dim3(256), 0, st, (const float*)hy->c, (long long)l.c_conv,
+                       (const float*)hy->beta, (const float*)hy->decay, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, H, G, dk, dv));
+      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
+                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv));
+      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, nullptr, T, D, l.n_o, hy->m1, st, &y1));
+    } else {
+      const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
+      const int Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
+      XB_TRY(hy_launch(e, hy_kv_append_kernel<KT>, dim3(T), dim3(256), 0, st, P, l.off_k, l.off_v, (KT*)l.k_pool, (KT*)l.v_pool, m, G, dk, dv));
+      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT>, dim3(T, (H + 3) / 4), dim3(128), (size_t)4 * dk * sizeof(float), st, P, l.off_q,
+                       l.off_g, (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f,
+                       a1, (long long)l.n_o));
+      const long long ldc = 2LL * Hr * rk + (long long)Hr * rv;
+      XB_TRY(hy_launch(e, hy_hgrn_prep_kernel, dim3(T), dim3(256), 0, st, P, l.off_rq, l.off_rf, l.off_rv, (const float*)l.lower, hy->c,
+                       ldc, Hr * rk, Hr * rv));
+      XB_TRY(hy_launch(e, hy_hgrn_kernel, dim3(n_seqs, Hr, (rv + 7) / 8), dim3(256), 0, st, (const float*)hy->c, ldc,
+                       hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, Hr, rk, rv));
+      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o2,
+                       (const float*)l.head_norm, P, -1, d.norm_eps, 1.0f, a2, (long long)l.n_o2, Hr, rv));
+      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, nullptr, T, D, l.n_o, hy->m1, st, &y1));
+      XB_TRY(hy_linear<AT>(e, a2, l.n_o2, l.w_o2, nullptr, T, D, l.n_o2, hy->m2, st, &y2));
+      s1 = c.left_scale;
+      s2 = c.right_scale;
+    }
+    // x += norm1b(mixer); then whatever reads x next
+    XB_TRY(hy_row_op<AT>(e, T, y1, s1, y2, s2, l.norm1b, 1.f, has_ff ? l.norm2 : (has_side ? nullptr : next_norm),
+                         (!has_ff && has_side) ? (void*)a1 : nullptr, st));
+    if (has_ff) {
+      LinOut u, dn;
+      XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, l.canon2, l.st_canon2, m, st));
+      XB_TRY(hy_linear<AT>(e, a1, D, l.w_up, nullptr, T, c.ff, D, hy->P, st, &u));
+      const long long n = (long long)T * c.ff;
+      XB_TRY(hy_launch(e, hy_relu2_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, u, a1, (long long)c.ff, T, c.ff));
+      XB_TRY(hy_linear<AT>(e, a1, c.ff, l.w_down, nullptr, T, D, c.ff, hy->m1, st, &dn));
+      XB_TRY(hy_row_op<AT>(e, T, dn, 1.f, hy_none(), 0.f, l.norm2b, 1.f, has_side ? nullptr : next_norm, has_side ? (void*)a1 : nullptr, st));
+    }
+    if (has_side) {
+      LinOut gt, yy;
+      const int sd = d.side_dim;
+      XB_TRY(hy_linear<AT>(e, a1, D, l.w_sgate, nullptr, T, sd, D, hy->P, st, &gt));
+      const long long n = (long long)T * sd;
+      XB_TRY(hy_launch(e, hy_side_gate_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, gt, (const int*)e->in_tokens,
+                       (const bf16*)hy->side_embed, (long long)sd * d.n_layers, li * sd, d.vocab, a2, (long long)sd, T, sd));
+      XB_TRY(hy_linear<AT>(e, a2, sd, l.w_sproj, nullptr, T, D, sd, hy->m1, st, &yy));
+      XB_TRY(hy_row_op<AT>(e, T, yy, 1.f, hy_none(), 0.f, l.side_norm, 0.f, next_norm, nullptr, st));
+    }
+    if (taps != nullptr && taps[li] != nullptr)
+      XB_CUDA(cudaMemcpyAsync(taps[li], hy->x, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  }
+  if (with_head) {
+    const int n = e->sel_rows != nullptr ? e->sel_n : n_seqs;
+    if (n > 0) {
+      const int* idx = e->sel_rows != nullptr ? hy->d_rows : m.seq_last;
+      LinOut y;
+      XB_TRY(hy_launch(e, hy_gather_rows_kernel<AT>, dim3(n), dim3(256), 0, st, (const float*)hy->hn, idx, reinterpret_cast<AT*>(hy->head_in), D));
+      XB_TRY(hy_linear<AT>(e, hy->head_in, D, hy->head, nullptr, n, d.vocab, D, hy->head_raw, st, &y));
+      const long long tot = (long long)n * d.vocab;
+      XB_TRY(hy_launch(e, hy_logits_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, st, y, d.logit_softcap, e->logits, n, d.vocab));
+    }
+  }
+  return 0;
+}
+
+static int hy_run_body(xb_engine* e, int T, int n_seqs, void* const* taps, cudaStream_t st, int with_head) {
+  if (e->hy->d.compute_fp32) return hy_run_body_t<float>(e, T, n_seqs, taps, st, with_head);
+  return hy_run_body_t<bf16>(e, T, n_seqs, taps, st, with_head);
+}

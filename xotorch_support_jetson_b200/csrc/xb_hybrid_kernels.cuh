@@ -1,0 +1,599 @@
+// Kernels of the hybrid layer kinds (xb_hybrid_layer in xb200.h): gated delta rule, HGRN2, windowed softmax attention
+// with kept first tokens and an output gate, causal per-channel filters with a carried tail, fp32 residual + RMS norms,
+// squared-ReLU feed-forward, per-layer token side input, soft-capped logits.
+//
+// Precision: the residual stream, norms, attention scores and weights, gates, decays, unit norms and the recurrent
+// state are fp32 everywhere.  AT is the type a Linear READS: bf16 (serving) or float (the all-fp32 mode, no TF32:
+// plain FMA).  Every Linear's output is consumed through LinOut, which hides whether it is one fp32 matrix, fp32
+// split-K planes of the tcgen05 kernel, or a bf16 matrix.
+//
+// Per-sequence state lives in slots: a sequence that starts at position 0 finds zero state whatever the slot held
+// before (kernels test the position instead of clearing memory).
+#pragma once
+#include "xb_common.cuh"
+#include "xb_kernels.cuh"
+#include <math.h>
+
+#define HY_MAX_TAPS 16   // causal filters keep taps - 1 inputs per sequence
+#define HY_MAX_KREG 8    // recurrent state: a warp owns one value column, lane l holds rows l, l + 32, ... (key dim <= 256)
+
+struct LinOut {
+  const float* f;      // fp32 [planes][T][ld] (planes summed per column, see SplitInfo), or nullptr
+  const bf16* h;       // bf16 [T][ld], or nullptr
+  SplitInfo si;        // si.splits == 0: one plane
+  long long plane;     // floats between planes
+  long long ld;
+};
+
+__device__ __forceinline__ float lin_at(const LinOut& o, long long row, int col) {
+  if (o.h != nullptr) return bf2f(o.h[row * o.ld + col]);
+  const float* p = o.f + row * o.ld + col;
+  if (o.si.splits == 0) return *p;
+  const int n = xb_n_segments(o.si, col);
+  float s = 0.f;
+  for (int i = 0; i < n; ++i) s += p[i * o.plane];
+  return s;
+}
+
+template <typename AT> __device__ __forceinline__ void act_store(AT* p, float v);
+template <> __device__ __forceinline__ void act_store<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void act_store<bf16>(bf16* p, float v) { *p = f2bf(v); }
+template <typename AT> __device__ __forceinline__ float act_load(const AT* p);
+template <> __device__ __forceinline__ float act_load<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float act_load<bf16>(const bf16* p) { return bf2f(*p); }
+
+__device__ __forceinline__ float hy_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float hy_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float hy_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float hy_gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// first row, length, first position and slot of the sequence with index s
+struct SeqSpan { int start, len, pos0, slot; };
+__device__ __forceinline__ SeqSpan seq_span(const BatchMeta& m, int s) {
+  SeqSpan r;
+  r.start = s > 0 ? m.seq_last[s - 1] + 1 : 0;
+  r.len = m.seq_last[s] - r.start + 1;
+  r.pos0 = m.tok_pos[r.start];
+  r.slot = m.seq_slot[s];
+  return r;
+}
+
+// ----------------------------------------------------------------------------- embedding
+__global__ void hy_embed_kernel(const int* __restrict__ tokens, const bf16* __restrict__ emb, float* __restrict__ x, int D, int V) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) x[(long long)t * D + i] = bf2f(emb[(long long)tok * D + i]);
+}
+
+// ----------------------------------------------------------------------------- residual + norms, one block per row
+// m   = s1 * m1 + s2 * m2                         (branch output; absent when m1 has no data)
+// x  += m / rms(m) * (bw + bw_one)                (bw_one = 1: weight stored as an offset from one; 0: plain weight)
+// hn  = x / rms(x) * (1 + nw)                     (the next reader's norm; skipped when nw == nullptr)
+// xa  = x as a Linear input                       (skipped when xa == nullptr)
+struct RowOpArgs {
+  float* x;
+  LinOut m1, m2;
+  float s1, s2;
+  const float* bw;
+  float bw_one;
+  const float* nw;
+  float* hn;
+  void* xa;
+  float eps;
+  int D;
+};
+
+template <typename AT, int NT>
+__global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const int D = a.D;
+  float* x = a.x + t * D;
+  const bool branch = a.m1.f != nullptr || a.m1.h != nullptr;
+  const bool two = a.m2.f != nullptr || a.m2.h != nullptr;
+  if (branch) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += NT) {
+      float v = a.s1 * lin_at(a.m1, t, i);
+      if (two) v += a.s2 * lin_at(a.m2, t, i);
+      row[i] = v;
+      ss += v * v;
+    }
+    ss = block_sum<NT>(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < D; i += NT) {
+      const float v = x[i] + row[i] * inv * (a.bw[i] + a.bw_one);
+      x[i] = v;
+      row[i] = v;
+      s2 += v * v;
+    }
+    if (a.nw == nullptr && a.xa == nullptr) return;
+    s2 = block_sum<NT>(s2, red);
+    if (a.nw != nullptr) {
+      const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
+      for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * (1.0f + a.nw[i]);
+    }
+  } else {
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < D; i += NT) {
+      const float v = x[i];
+      row[i] = v;
+      s2 += v * v;
+    }
+    s2 = block_sum<NT>(s2, red);
+    if (a.nw != nullptr) {
+      const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
+      for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * (1.0f + a.nw[i]);
+    }
+  }
+  if (a.xa != nullptr) {
+    AT* xa = reinterpret_cast<AT*>(a.xa) + t * D;
+    for (int i = threadIdx.x; i < D; i += NT) act_store<AT>(xa + i, row[i]);
+  }
+}
+
+// ----------------------------------------------------------------------------- causal per-channel filter
+// out[t, c] = (identity ? in[t, c] : 0) + sum_j w[c, j] * in[t - (taps-1-j), c], optionally through SiLU.  Inputs of
+// earlier calls come from the slot's tail (the last taps-1 inputs, oldest first); inputs before position 0 are zero.
+template <typename OT>
+__global__ void hy_taps_kernel(LinOut in, int col0, int C, int taps, const float* __restrict__ w, const float* __restrict__ tail,
+                               long long tail_stride, BatchMeta m, int identity, int act_silu, OT* __restrict__ out, long long ld_out) {
+  const int row = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s = m.tok_seq[row];
+  const int start = s > 0 ? m.seq_last[s - 1] + 1 : 0;
+  const int pos = m.tok_pos[row], pos0 = m.tok_pos[start];
+  const float* tl = tail + (long long)m.seq_slot[s] * tail_stride;
+  float acc = identity ? lin_at(in, row, col0 + c) : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int back = taps - 1 - j;
+    const int p = pos - back;
+    if (p < 0) continue;
+    float v;
+    if (row - back >= start) v = lin_at(in, row - back, col0 + c);
+    else v = tl[(long long)(p - (pos0 - (taps - 1))) * C + c];
+    acc += w[(long long)c * taps + j] * v;
+  }
+  if (act_silu) acc = hy_silu(acc);
+  act_store<OT>(out + (long long)row * ld_out + c, acc);
+}
+
+// the slot's tail after this call: the last taps-1 inputs of the sequence, oldest first (runs after hy_taps_kernel)
+__global__ void hy_tail_update_kernel(LinOut in, int col0, int C, int taps, float* __restrict__ tail, long long tail_stride, BatchMeta m) {
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const SeqSpan sp = seq_span(m, s);
+  float* tl = tail + (long long)sp.slot * tail_stride;
+  float keep[HY_MAX_TAPS];
+  const int end = sp.pos0 + sp.len;
+  for (int j = 0; j < taps - 1; ++j) {
+    const int p = end - (taps - 1) + j;
+    float v = 0.f;
+    if (p >= sp.pos0) v = lin_at(in, sp.start + (p - sp.pos0), col0 + c);
+    else if (p >= 0) v = tl[(long long)(p - (sp.pos0 - (taps - 1))) * C + c];
+    keep[j] = v;
+  }
+  for (int j = 0; j < taps - 1; ++j) tl[(long long)j * C + c] = keep[j];
+}
+
+// ----------------------------------------------------------------------------- Linear for any shape
+// y[T, N] (fp32) = x[T, K] w[N, K]^T + bias.  Weights bf16 row-major, accumulation fp32 (plain FMA).
+// Few rows (decode): a warp per output feature streams the weight row once for all rows.
+#define HY_SMALL_T 8
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_linear_small_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                                                              const float* __restrict__ bias, float* __restrict__ y, long long ldy,
+                                                              int T, int N, int K) {
+  const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (n >= N) return;
+  float acc[HY_SMALL_T];
+#pragma unroll
+  for (int t = 0; t < HY_SMALL_T; ++t) acc[t] = 0.f;
+  const bf16* wr = w + (long long)n * K;
+  if ((K & 7) == 0 && (reinterpret_cast<uintptr_t>(wr) & 15) == 0) {
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 u = *reinterpret_cast<const uint4*>(wr + k);
+      const float2 w0 = bf2_to_f2(u.x), w1 = bf2_to_f2(u.y), w2 = bf2_to_f2(u.z), w3 = bf2_to_f2(u.w);
+      const float wv[8] = {w0.x, w0.y, w1.x, w1.y, w2.x, w2.y, w3.x, w3.y};
+#pragma unroll
+      for (int t = 0; t < HY_SMALL_T; ++t) {
+        if (t < T) {
+          const AT* xr = x + (long long)t * ldx + k;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[t] = fmaf(wv[j], act_load<AT>(xr + j), acc[t]);
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float wv = bf2f(wr[k]);
+#pragma unroll
+      for (int t = 0; t < HY_SMALL_T; ++t)
+        if (t < T) acc[t] = fmaf(wv, act_load<AT>(x + (long long)t * ldx + k), acc[t]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < HY_SMALL_T; ++t) {
+    if (t < T) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) y[(long long)t * ldy + n] = v + (bias != nullptr ? bias[n] : 0.f);
+    }
+  }
+}
+
+// Many rows: 64 x 64 output tile per block, 16-deep k slices through shared memory, 4 x 4 outputs per thread.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_linear_tiled_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                                                              const float* __restrict__ bias, float* __restrict__ y, long long ldy,
+                                                              int T, int N, int K) {
+  __shared__ float xs[16][68];
+  __shared__ float ws[16][68];
+  const int t0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = threadIdx.x + e * 256;   // 0..1023 = 64 rows x 16 k
+      const int r = idx >> 4, kk = idx & 15;
+      const int k = k0 + kk;
+      float xv = 0.f, wv = 0.f;
+      if (k < K) {
+        if (t0 + r < T) xv = act_load<AT>(x + (long long)(t0 + r) * ldx + k);
+        if (n0 + r < N) wv = bf2f(w[(long long)(n0 + r) * K + k]);
+      }
+      xs[kk][r] = xv;
+      ws[kk][r] = wv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + ty * 4 + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) y[(long long)t * ldy + n] = acc[i][j] + (bias != nullptr ? bias[n] : 0.f);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- gated delta rule
+// Inputs per token: q, k (kv_heads x dk) and v (heads x dv) after the short filter + SiLU, in `c` [T, 2*G*dk + H*dv];
+// the fused projection P also carries the read-out gate (H*dv), b (H) and a (H) columns.
+// Prep, one block per token: q and k to unit length per head (q also times dk^-1/2), beta = sigmoid(b),
+// decay = exp(-exp(A_log) * softplus(a + dt_bias)).
+__global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ c, long long ldc, LinOut P, int off_b, int off_a,
+                                                            const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                            float* __restrict__ beta, float* __restrict__ decay, int H, int G, int dk) {
+  const long long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float* row = c + t * ldc;
+  for (int u = warp; u < 2 * G; u += nw) {   // u < G: q head u; else k head u - G (q block, then k block)
+    float* p = row + (long long)u * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss += p[i] * p[i];
+    ss = warp_sum(ss);
+    float sc = 1.0f / sqrtf(ss + 1e-6f);
+    if (u < G) sc *= 1.0f / sqrtf((float)dk);
+    for (int i = lane; i < dk; i += 32) p[i] *= sc;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    beta[t * H + h] = hy_sigmoid(lin_at(P, t, off_b + h));
+    decay[t * H + h] = expf(-expf(A_log[h]) * hy_softplus(lin_at(P, t, off_a + h) + dt_bias[h]));
+  }
+}
+
+// Recurrence.  Per head the state is S [dk, dv]; every value column evolves alone:
+//   S_j <- g S_j;  u_j = beta (v_j - k . S_j);  S_j <- S_j + k u_j;  o_j = q . S_j
+// so a warp owns one column (lane l holds rows l, l+32, ...), and with a = k . S_j, b = q . S_j, qk = q . k taken on
+// the OLD column in one reduction: u_j = beta (v_j - g a), o_j = g b + qk u_j.
+// grid (n_seqs, H, ceil(dv / warps)); state [slot][H][dv][dk] fp32.
+__global__ void __launch_bounds__(256) hy_delta_rule_kernel(const float* __restrict__ c, long long ldc, const float* __restrict__ beta,
+                                                            const float* __restrict__ decay, float* __restrict__ state,
+                                                            long long state_stride, float* __restrict__ o, long long ldo, BatchMeta m,
+                                                            int H, int G, int dk, int dv) {
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.z * (blockDim.x >> 5) + warp;
+  if (j >= dv) return;
+  const SeqSpan sp = seq_span(m, s);
+  const int g = h / (H / G);
+  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + j) * dk;
+  float S[HY_MAX_KREG];
+#pragma unroll
+  for (int i = 0; i < HY_MAX_KREG; ++i) {
+    const int r = lane + 32 * i;
+    S[i] = (sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
+  }
+  const long long qoff = (long long)g * dk, koff = (long long)(G + g) * dk, voff = (long long)2 * G * dk + (long long)h * dv + j;
+  for (int t = 0; t < sp.len; ++t) {
+    const long long row = sp.start + t;
+    const float* cr = c + row * ldc;
+    float qv[HY_MAX_KREG], kv[HY_MAX_KREG];
+    float a = 0.f, b = 0.f, qk = 0.f;
+#pragma unroll
+    for (int i = 0; i < HY_MAX_KREG; ++i) {
+      const int r = lane + 32 * i;
+      qv[i] = r < dk ? cr[qoff + r] : 0.f;
+      kv[i] = r < dk ? cr[koff + r] : 0.f;
+      a = fmaf(kv[i], S[i], a);
+      b = fmaf(qv[i], S[i], b);
+      qk = fmaf(qv[i], kv[i], qk);
+    }
+    const float v = cr[voff], be = beta[row * H + h], gd = decay[row * H + h];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      a += __shfl_xor_sync(0xffffffffu, a, off);
+      b += __shfl_xor_sync(0xffffffffu, b, off);
+      qk += __shfl_xor_sync(0xffffffffu, qk, off);
+    }
+    const float u = be * (v - gd * a);
+#pragma unroll
+    for (int i = 0; i < HY_MAX_KREG; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
+    if (lane == 0) o[row * ldo + (long long)h * dv + j] = fmaf(qk, u, gd * b);
+  }
+#pragma unroll
+  for (int i = 0; i < HY_MAX_KREG; ++i) {
+    const int r = lane + 32 * i;
+    if (r < dk) st[r] = S[i];
+  }
+}
+
+// ----------------------------------------------------------------------------- HGRN2
+// Prep: q = silu(.), f = lower + (1 - lower) sigmoid(.), v copied, into one fp32 row [q | f | v].
+__global__ void hy_hgrn_prep_kernel(LinOut P, int off_q, int off_f, int off_v, const float* __restrict__ lower, float* __restrict__ c,
+                                    long long ldc, int HK, int HV) {
+  const long long t = blockIdx.x;
+  float* row = c + t * ldc;
+  for (int i = threadIdx.x; i < 2 * HK + HV; i += blockDim.x) {
+    float v;
+    if (i < HK) v = hy_silu(lin_at(P, t, off_q + i));
+    else if (i < 2 * HK) {
+      const float lo = lower[i - HK];
+      v = lo + (1.0f - lo) * hy_sigmoid(lin_at(P, t, off_f + i - HK));
+    } else v = lin_at(P, t, off_v + i - 2 * HK);
+    row[i] = v;
+  }
+}
+
+// Recurrence per head: S <- diag(f) S + (1 - f) v^T, o = S^T q.  Column j: S_j <- f * S_j + (1 - f) v_j, o_j = q . S_j.
+__global__ void __launch_bounds__(256) hy_hgrn_kernel(const float* __restrict__ c, long long ldc, float* __restrict__ state,
+                                                      long long state_stride, float* __restrict__ o, long long ldo, BatchMeta m, int H,
+                                                      int dk, int dv) {
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.z * (blockDim.x >> 5) + warp;
+  if (j >= dv) return;
+  const SeqSpan sp = seq_span(m, s);
+  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + j) * dk;
+  float S[HY_MAX_KREG];
+#pragma unroll
+  for (int i = 0; i < HY_MAX_KREG; ++i) {
+    const int r = lane + 32 * i;
+    S[i] = (sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
+  }
+  const long long HK = (long long)H * dk;
+  const long long qoff = (long long)h * dk, foff = HK + (long long)h * dk, voff = 2 * HK + (long long)h * dv + j;
+  for (int t = 0; t < sp.len; ++t) {
+    const long long row = sp.start + t;
+    const float* cr = c + row * ldc;
+    const float v = cr[voff];
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < HY_MAX_KREG; ++i) {
+      const int r = lane + 32 * i;
+      if (r < dk) {
+        const float f = cr[foff + r];
+        S[i] = fmaf(f, S[i], (1.0f - f) * v);
+        acc = fmaf(cr[qoff + r], S[i], acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) o[row * ldo + (long long)h * dv + j] = acc;
+  }
+#pragma unroll
+  for (int i = 0; i < HY_MAX_KREG; ++i) {
+    const int r = lane + 32 * i;
+    if (r < dk) st[r] = S[i];
+  }
+}
+
+// ----------------------------------------------------------------------------- per-head RMS norm (+ SiLU gate) of a read-out
+// out[t, h*dv + j] = scale * o / rms_over_dv(o) * w[j] * (gate ? silu(P[t, off_gate + h*dv + j]) : 1)
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_head_norm_kernel(const float* __restrict__ o, long long ldo, const float* __restrict__ w,
+                                                           LinOut P, int off_gate, float eps, float scale, AT* __restrict__ out,
+                                                           long long ld_out, int H, int dv) {
+  const long long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nw) {
+    const float* p = o + t * ldo + (long long)h * dv;
+    float ss = 0.f;
+    for (int j = lane; j < dv; j += 32) ss += p[j] * p[j];
+    ss = warp_sum(ss);
+    const float inv = scale / sqrtf(ss / (float)dv + eps);
+    for (int j = lane; j < dv; j += 32) {
+      float v = p[j] * inv * w[j];
+      if (off_gate >= 0) v *= hy_silu(lin_at(P, t, off_gate + h * dv + j));
+      act_store<AT>(out + t * ld_out + (long long)h * dv + j, v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- windowed softmax attention
+// Paged pools [n_pages][G][page_tokens][d] of KT (bf16 serving, float in the all-fp32 mode).
+template <typename KT>
+__global__ void hy_kv_append_kernel(LinOut P, int off_k, int off_v, KT* __restrict__ k_pool, KT* __restrict__ v_pool, BatchMeta m,
+                                    int G, int dk, int dv) {
+  const int row = blockIdx.x;
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  const int page = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
+  const int in_page = pos % m.page_tokens;
+  for (int i = threadIdx.x; i < G * (dk + dv); i += blockDim.x) {
+    if (i < G * dk) {
+      const int g = i / dk, d = i - g * dk;
+      act_store<KT>(k_pool + (((long long)page * G + g) * m.page_tokens + in_page) * dk + d, lin_at(P, row, off_k + i));
+    } else {
+      const int i2 = i - G * dk;
+      const int g = i2 / dv, d = i2 - g * dv;
+      act_store<KT>(v_pool + (((long long)page * G + g) * m.page_tokens + in_page) * dv + d, lin_at(P, row, off_v + i2));
+    }
+  }
+}
+
+// One warp per (token, query head).  Query i sees key j when j <= i and (i - j < window or j < keep_first): the kept
+// first keys, then the window, 32 keys at a time: a lane scores one key (fp32 dot with the query in shared memory),
+// the warp does the online softmax, then lanes own value channels for the weighted sum.  No rotation: positions
+// enter through the mask only.  The epilogue multiplies by sigmoid(gate column) and `out_scale`.
+// dv <= 256.  Dynamic shared memory: warps * dk floats.
+template <typename KT, typename AT>
+__global__ void __launch_bounds__(128) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
+                                                             const KT* __restrict__ v_pool, BatchMeta m, int H, int G, int dk, int dv,
+                                                             int window, int keep_first, float scale, float out_scale,
+                                                             AT* __restrict__ out, long long ld_out) {
+  extern __shared__ float qsm[];
+  const int row = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (h >= H) return;
+  float* q = qsm + warp * dk;
+  for (int i = lane; i < dk; i += 32) q[i] = lin_at(P, row, off_q + h * dk + i) * scale;
+  __syncwarp();
+  const int g = h / (H / G);
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  const int* pages = m.page_table + (long long)m.seq_slot[s] * m.max_pages;
+  const int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
+  const int n_first = keep_first < lo ? keep_first : lo;   // kept keys that the window does not already cover
+  const int n_vis = n_first + (pos - lo + 1);
+  float mx = -INFINITY, l = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  for (int base = 0; base < n_vis; base += 32) {
+    const int idx = base + lane;
+    float sc = -INFINITY;
+    long long prow = 0;
+    if (idx < n_vis) {
+      const int kp = idx < n_first ? idx : lo + (idx - n_first);
+      prow = ((long long)pages[kp / m.page_tokens] * G + g) * m.page_tokens + kp % m.page_tokens;
+      const KT* kr = k_pool + prow * dk;
+      float d = 0.f;
+      for (int i = 0; i < dk; ++i) d = fmaf(q[i], act_load<KT>(kr + i), d);
+      sc = d;
+    }
+    const float tmax = warp_max(sc);
+    const float nm = fmaxf(mx, tmax);
+    const float corr = expf(mx - nm);   // mx = -inf on the first tile: exp(-inf) = 0
+    const float p = idx < n_vis ? expf(sc - nm) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] *= corr;
+    mx = nm;
+    const int cnt = n_vis - base < 32 ? n_vis - base : 32;
+    for (int jj = 0; jj < cnt; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const long long pr = __shfl_sync(0xffffffffu, prow, jj);
+      const KT* vr = v_pool + pr * dv;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int d = lane + 32 * c;
+        if (d < dv) acc[c] = fmaf(pj, act_load<KT>(vr + d), acc[c]);
+      }
+    }
+  }
+  const float inv = out_scale / l;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int d = lane + 32 * c;
+    if (d < dv) {
+      float v = acc[c] * inv;
+      if (off_gate >= 0) v *= hy_sigmoid(lin_at(P, row, off_gate + h * dv + d));
+      act_store<AT>(out + (long long)row * ld_out + (long long)h * dv + d, v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- feed-forward activation, side input, logits
+template <typename AT>
+__global__ void hy_relu2_kernel(LinOut u, AT* __restrict__ out, long long ld_out, int T, int F) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * F) return;
+  const long long t = idx / F;
+  const int i = (int)(idx - t * F);
+  const float v = fmaxf(lin_at(u, t, i), 0.f);
+  act_store<AT>(out + t * ld_out + i, v * v);
+}
+
+// g[t, i] = gelu_tanh(gate[t, i]) * side_embed[token[t], col0 + i]
+template <typename AT>
+__global__ void hy_side_gate_kernel(LinOut gate, const int* __restrict__ tokens, const bf16* __restrict__ side_embed, long long ld_se,
+                                    int col0, int V, AT* __restrict__ out, long long ld_out, int T, int sd) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * sd) return;
+  const long long t = idx / sd;
+  const int i = (int)(idx - t * sd);
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  act_store<AT>(out + t * ld_out + i, hy_gelu_tanh(lin_at(gate, t, i)) * bf2f(side_embed[(long long)tok * ld_se + col0 + i]));
+}
+
+// rows idx[r] of the normed stream as the head's input
+template <typename AT>
+__global__ void hy_gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ idx, AT* __restrict__ dst, int D) {
+  const int r = blockIdx.x;
+  const float* s = src + (long long)idx[r] * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) act_store<AT>(dst + (long long)r * D + i, s[i]);
+}
+
+// logits <- cap * tanh(logits / cap) (cap > 0), from any Linear output into a dense fp32 [n, V]
+__global__ void hy_logits_kernel(LinOut y, float cap, float* __restrict__ out, int n, int V) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * V) return;
+  const long long t = idx / V;
+  const int i = (int)(idx - t * V);
+  const float v = lin_at(y, t, i);
+  out[idx] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+// ----------------------------------------------------------------------------- loader: any supported source type -> fp32 / bf16, strided rows
+// src element types: 0 bf16, 1 fp16, 2 fp32 (the loader's codes).  rows x cols, destination row pitch ld_dst.
+__device__ __forceinline__ float hy_src_at(const void* src, long long i, int dt) {
+  if (dt == 0) return bf2f(reinterpret_cast<const bf16*>(src)[i]);
+  if (dt == 1) return __half2float(reinterpret_cast<const __half*>(src)[i]);
+  return reinterpret_cast<const float*>(src)[i];
+}
+template <typename OT>
+__global__ void hy_load_convert_kernel(const void* __restrict__ src, int dt, long long rows, long long cols, OT* __restrict__ dst,
+                                       long long ld_dst) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * cols) return;
+  const long long r = idx / cols, c = idx - r * cols;
+  act_store<OT>(dst + r * ld_dst + c, hy_src_at(src, idx, dt));
+}

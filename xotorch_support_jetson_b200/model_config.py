@@ -28,9 +28,63 @@ _DIRECT_FIELDS = (
 _OPTIONAL_FIELDS = (("attention_dropout", "attn_dropout", 0.0), ("attention_bias", "attn_bias", False), ("hidden_act", "hidden_act", "silu"))
 
 
+HYBRID_ARCHITECTURES = ("Refatar",)
+
+
+def is_hybrid(config: dict) -> bool:
+  """True for configs of per-layer-described models (``hybrid_model_config``), which run on the hybrid engine."""
+  return config.get("family") == "hybrid"
+
+
+def hybrid_model_config(raw: dict) -> dict:
+  """A Refatar ``config.json`` (``architecture``, ``width``, ``vocab``, ``layers`` [{type, mixer, mlp}], ``norm.eps``,
+  optional ``canon.taps``, ``token_side.dim``, ``logit_softcap``) -> the engine's dict.  Every size and constant comes from
+  the file; what the file does not mention is switched off.  The keys the Llama-shaped path uses (``embed_dim``,
+  ``vocab_size``, ``num_layers``, ``max_seq_len``) are filled so that the serving code above the stage needs no branch.
+
+  Layer kinds: ``delta`` = gated delta rule {heads, kv_heads, dim, vdim, conv}; ``parallel`` = {left: windowed softmax
+  attention {heads, kv_heads, dim, vdim, scale, mask{size, keep_first}}, right: HGRN2 {heads, dim, vdim}, left_scale,
+  right_scale}; ``mlp`` = {kind: dense, ff} or null."""
+  arch = raw.get("architecture")
+  if arch not in HYBRID_ARCHITECTURES:
+    raise ValueError(f"unknown architecture {arch!r}")
+  layers = []
+  for i, lc in enumerate(raw["layers"]):
+    mx, kind = lc["mixer"], lc["type"]
+    if kind == "delta":
+      lay = {"mixer": "delta", "heads": int(mx["heads"]), "kv_heads": int(mx["kv_heads"]), "dim": int(mx["dim"]),
+             "vdim": int(mx["vdim"]), "taps": int(mx["conv"])}
+    elif kind == "parallel":
+      le, ri = mx["left"], mx["right"]
+      lay = {"mixer": "parallel",
+             "left": {"heads": int(le["heads"]), "kv_heads": int(le["kv_heads"]), "dim": int(le["dim"]), "vdim": int(le["vdim"]),
+                      "scale": float(le["scale"]), "window": int(le["mask"]["size"]), "keep_first": int(le["mask"]["keep_first"])},
+             "right": {"heads": int(ri["heads"]), "dim": int(ri["dim"]), "vdim": int(ri["vdim"])},
+             "left_scale": float(mx["left_scale"]), "right_scale": float(mx["right_scale"])}
+    else:
+      raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    mlp = lc.get("mlp")
+    if mlp is not None and mlp.get("kind", "dense") != "dense":
+      raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+    lay["ff"] = int(mlp["ff"]) if mlp is not None else 0
+    layers.append(lay)
+  canon, side = raw.get("canon"), raw.get("token_side")
+  return {
+    "family": "hybrid", "architecture": arch,
+    "embed_dim": int(raw["width"]), "vocab_size": int(raw["vocab"]), "num_layers": len(layers),
+    "max_seq_len": int(raw.get("max_seq_len", 1 << 20)), "norm_eps": float(raw["norm"]["eps"]),
+    "taps": int(canon["taps"]) if canon else 0, "side_dim": int(side["dim"]) if side else 0,
+    "logit_softcap": float(raw.get("logit_softcap") or 0.0), "layers": layers,
+    "torch_dtype": HF_PRECISION_STR_TO_DTYPE.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16),
+  }
+
+
 def load_model_config(model_config_path: Path) -> dict:
-  """Read an HF ``config.json`` into the flat dict the engine works with."""
+  """Read a ``config.json`` into the flat dict the engine works with: an HF Llama-shaped one, or (key ``architecture``
+  naming a hybrid design) a per-layer description."""
   hf = json.loads(Path(model_config_path).read_text())
+  if hf.get("architecture") in HYBRID_ARCHITECTURES:
+    return hybrid_model_config(hf)
   cfg = {ours: hf[theirs] for theirs, ours in _DIRECT_FIELDS}
   cfg.update({ours: hf.get(theirs, default) for theirs, ours, default in _OPTIONAL_FIELDS})
   cfg["head_dim"] = hf.get("head_dim", hf["hidden_size"] // hf["num_attention_heads"])

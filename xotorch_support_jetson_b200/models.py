@@ -50,6 +50,37 @@ def _mistral(hidden, heads, kv, inter, layers, head_dim, vocab=32768):
   }
 
 
+def _refatar(width, vocab, layers, taps=4, side=8, softcap=30.0, eps=1e-5):
+  """A Refatar config.json: layers is a list of ("delta", {heads, kv_heads, dim, vdim, conv}, ff) /
+  ("parallel", {left, right, left_scale, right_scale}, ff) entries (ff 0 = no feed-forward)."""
+  cfg = {"architecture": "Refatar", "width": width, "vocab": vocab, "norm": {"eps": eps},
+         "layers": [{"type": t, "mixer": m, "mlp": ({"kind": "dense", "ff": ff} if ff else None)} for t, m, ff in layers]}
+  if taps:
+    cfg["canon"] = {"taps": taps}
+  if side:
+    cfg["token_side"] = {"dim": side}
+  if softcap:
+    cfg["logit_softcap"] = softcap
+  return cfg
+
+
+def _refatar_pair(heads, kv, dim, vdim, window, keep, r_heads, r_dim, r_vdim):
+  return {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+                   "mask": {"size": window, "keep_first": keep}},
+          "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim}, "left_scale": 1.0, "right_scale": 1.0}
+
+
+_REFATAR_TINY = _refatar(128, 512, [
+  ("delta", {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 48, "conv": 3}, 256),
+  ("parallel", _refatar_pair(4, 2, 32, 48, 24, 3, 2, 32, 64), 256),
+  ("parallel", _refatar_pair(8, 8, 16, 16, 9, 0, 4, 16, 32), 0),
+  ("delta", {"heads": 2, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 4}, 192),
+], taps=3, side=8)
+# 1B-class geometry for throughput runs (random weights): the widths of llama-3.2-1b with alternating mixers
+_REFATAR_1B = _refatar(2048, 128256, [
+  (("delta", {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}, 8192) if i % 2 == 0 else
+   ("parallel", _refatar_pair(32, 8, 64, 64, 1024, 4, 16, 128, 128), 8192)) for i in range(16)], taps=4, side=32)
+
 # model id -> {layers, repo:{EngineClassName: hf repo}, hf_config}
 model_cards = {
   "llama-3.2-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "unsloth/Llama-3.2-1B-Instruct"},
@@ -69,6 +100,8 @@ model_cards = {
                      "hf_config": _llama(512, 4, 2, 1024, 6, head_dim=128, factor=8.0, vocab=2048)},
   "qwen-2.5-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/qwen-2.5-tiny"},
                     "hf_config": _qwen(384, 6, 2, 768, 4, vocab=1536, max_pos=4096)},
+  "refatar-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/refatar-tiny"}, "hf_config": _REFATAR_TINY},
+  "refatar-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/refatar-1b"}, "hf_config": _REFATAR_1B},
   "mistral-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/mistral-tiny"},
                    "hf_config": _mistral(320, 5, 1, 640, 4, head_dim=64, vocab=1280)},
 }

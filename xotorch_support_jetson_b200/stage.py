@@ -15,7 +15,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from . import _cabi
-from .model_config import has_qkv_bias, load_model_config, model_family, rope_table, uses_tied_head
+from .model_config import has_qkv_bias, is_hybrid, load_model_config, model_family, rope_table, uses_tied_head
 from .shard import Shard
 
 
@@ -56,13 +56,21 @@ class StageRuntime:
   def __init__(self, shard: Shard, config: dict, device: int = 0, max_batch_tokens: int = 4096,
                max_seqs: int = 32, max_tokens_per_seq: int = 4096, page_tokens: int = 64,
                rope_table_bf16: bool = True, rmsnorm_two_round: bool = True, max_positions: Optional[int] = None,
-               first_from_mlp: bool = False, last_to_attn: bool = False):
+               first_from_mlp: bool = False, last_to_attn: bool = False, dtype: str = "bfloat16",
+               max_logit_rows: Optional[int] = None):
     if not torch.cuda.is_available():
       raise RuntimeError("B200 engine needs a CUDA device: there is no CPU fallback")
     self.lib = _cabi.load()
     self.shard = shard
     self.config = config
     self.device = torch.device("cuda", device)
+    self.hybrid = is_hybrid(config)
+    if self.hybrid:
+      self._init_hybrid(shard, config, device, max_batch_tokens, max_seqs, max_tokens_per_seq, page_tokens, dtype,
+                        max_logit_rows, first_from_mlp or last_to_attn)
+      return
+    if dtype != "bfloat16":
+      raise ValueError("the Llama-shaped engine computes in bfloat16 only")
     self.family = model_family(shard.model_id)
     self.tied = uses_tied_head(shard.model_id)
     self.qkv_bias = has_qkv_bias(shard.model_id, config)
@@ -101,6 +109,59 @@ class StageRuntime:
     self.ho_handles: Optional[tuple] = None
     self.ho_connected = False
     self.ho_sent: Dict[int, int] = {}
+
+  def _init_hybrid(self, shard, config, device, max_batch_tokens, max_seqs, max_tokens_per_seq, page_tokens, dtype,
+                   max_logit_rows, half_layers):
+    """A per-layer-described model (model_config.hybrid_model_config) on the hybrid engine: one full-model stage whose
+    slots hold the attention layers' KV pages, the recurrent state and the filter tails."""
+    if dtype not in ("bfloat16", "float32"):
+      raise ValueError(f"dtype {dtype!r}: bfloat16 or float32")
+    nl = config["num_layers"]
+    if shard.start_layer != 0 or shard.end_layer != nl - 1 or half_layers:
+      raise ValueError("a hybrid model runs as one full-model stage (its fp32 residual stream has no hand-off format)")
+    self.family, self.tied, self.qkv_bias = "hybrid", False, False
+    self.compute_dtype = dtype
+    self.max_seqs, self.max_batch_tokens, self.max_tokens_per_seq = max_seqs, max_batch_tokens, max_tokens_per_seq
+    self.max_positions = max_tokens_per_seq
+    self.max_logit_rows = int(max_logit_rows if max_logit_rows is not None else max_seqs)
+    lays = (_cabi.HybridLayer * nl)()
+    for i, lc in enumerate(config["layers"]):
+      L = lays[i]
+      L.ff = lc["ff"]
+      if lc["mixer"] == "delta":
+        L.mixer = _cabi.MIX_DELTA
+        L.d_heads, L.d_kv_heads, L.d_dim, L.d_vdim, L.d_taps = lc["heads"], lc["kv_heads"], lc["dim"], lc["vdim"], lc["taps"]
+      else:
+        le, ri = lc["left"], lc["right"]
+        L.mixer = _cabi.MIX_PARALLEL
+        L.a_heads, L.a_kv_heads, L.a_dim, L.a_vdim = le["heads"], le["kv_heads"], le["dim"], le["vdim"]
+        L.a_window, L.a_keep_first, L.a_scale = le["window"], le["keep_first"], le["scale"]
+        L.r_heads, L.r_dim, L.r_vdim = ri["heads"], ri["dim"], ri["vdim"]
+        L.left_scale, L.right_scale = lc["left_scale"], lc["right_scale"]
+    d = _cabi.hybrid_desc(
+      n_layers=nl, dim=config["embed_dim"], vocab=config["vocab_size"], taps=config["taps"], side_dim=config["side_dim"],
+      norm_eps=config["norm_eps"], logit_softcap=config["logit_softcap"], compute_fp32=int(dtype == "float32"),
+      max_batch_tokens=max_batch_tokens, max_seqs=max_seqs, max_logit_rows=self.max_logit_rows)
+    self.first_from_mlp = self.last_to_attn = False
+    self.is_first = self.is_last = True
+    self.desc, self._layers = d, lays
+    self._h = C.c_void_p()
+    _cabi.check(self.lib.xb_engine_create_hybrid(C.byref(d), lays, device, C.byref(self._h)))
+    _cabi.check(self.lib.xb_kv_reserve(self._h, max_seqs, max_tokens_per_seq, page_tokens))
+    self.page_tokens = page_tokens
+    self.dim, self.vocab = config["embed_dim"], config["vocab_size"]
+    self.ho_geometry = self.ho_handles = None
+    self.ho_connected = False
+    self.ho_sent = {}
+
+  def load_named(self, name: str, t: torch.Tensor):
+    """One tensor of a hybrid model by its checkpoint name (xb_load_named)."""
+    t = t.detach().contiguous()
+    code = {torch.bfloat16: _cabi.ST_BF16, torch.float16: _cabi.ST_F16, torch.float32: _cabi.ST_F32}.get(t.dtype)
+    if code is None:
+      t, code = t.to(torch.float32), _cabi.ST_F32
+    shape = (C.c_int64 * max(t.dim(), 1))(*(t.shape if t.dim() else (1,)))
+    _cabi.check(self.lib.xb_load_named(self._h, name.encode(), C.c_void_p(t.data_ptr()), code, shape, max(t.dim(), 1)))
 
   # -- lifetime
   def close(self):
@@ -164,7 +225,10 @@ class StageRuntime:
     t0 = time.perf_counter()
     if not native:
       idx = _SafetensorsIndex(path)
-      self.load_hf_tensors(idx.get, idx.has)
+      if self.hybrid:
+        self.load_state({k: idx.get(k) for k in idx.where})
+      else:
+        self.load_hf_tensors(idx.get, idx.has)
       return {"files": len(idx.files), "tensors": None, "bytes": None, "seconds": time.perf_counter() - t0}
     files = sorted(Path(path).glob("*.safetensors"))
     if not files:
@@ -187,13 +251,21 @@ class StageRuntime:
     return f"{n.value} missing: {buf.value.decode()}" if n.value else ""
 
   def load_state(self, state: Dict[str, torch.Tensor]):
+    if self.hybrid:
+      for name, t in state.items():
+        self.load_named(name, t)
+      missing = self.weights_missing()
+      if missing:
+        raise RuntimeError(f"state lacks weights of {self.shard}: {missing}")
+      return
     self.load_hf_tensors(state.__getitem__, state.__contains__)
 
   # -- compute
   def forward(self, slot_ids: Sequence[int], q_lens: Sequence[int], positions: Sequence[int],
               tokens: Optional[torch.Tensor] = None, hidden: Optional[torch.Tensor] = None,
               out: Optional[torch.Tensor] = None, taps: Optional[List[torch.Tensor]] = None,
-              handoff: Optional[tuple] = None, host_logits: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+              handoff: Optional[tuple] = None, host_logits: Optional[torch.Tensor] = None,
+              want_rows: Optional[Sequence[int]] = None) -> Optional[torch.Tensor]:
     """tokens: int32 [T] (first shard) / hidden: bf16 [T, D].  Returns bf16 [T, D] hidden
     or fp32 [n_seqs, V] logits (last shard).  Enqueued on the current torch stream.
     host_logits (last shard): pinned fp32 [n_seqs, V] CPU tensor the LM-head kernel also stores the
@@ -209,6 +281,18 @@ class StageRuntime:
     if hidden is not None:
       assert hidden.dtype == torch.bfloat16 and hidden.is_cuda and hidden.numel() == T * self.dim and hidden.is_contiguous()
       b.hidden_in = hidden.data_ptr()
+    if want_rows is not None:
+      # hybrid engines: logits of the named token rows of this batch, fp32 [len(want_rows), V] (None when empty: the
+      # step then only advances the cache and the state); taps are fp32 [T, D]
+      assert self.hybrid and handoff is None and host_logits is None
+      rows = (C.c_int32 * max(len(want_rows), 1))(*want_rows)
+      if out is None and len(want_rows):
+        out = torch.empty((len(want_rows), self.vocab), dtype=torch.float32, device=self.device)
+      tp = (C.c_void_p * len(taps))(*[t.data_ptr() if t is not None else None for t in taps]) if taps is not None else None
+      stream = torch.cuda.current_stream(self.device).cuda_stream
+      _cabi.check(self.lib.xb_forward_rows(self._h, C.byref(b), rows, len(want_rows), C.c_void_p(out.data_ptr()) if out is not None else None,
+                                           tp, C.c_void_p(stream)))
+      return out
     sends = handoff is not None and handoff[2] >= 0
     if out is None and not sends:
       if self.is_last:
