@@ -139,8 +139,9 @@ class B200ShardInferenceEngine(InferenceEngine):
   def __init__(self, shard_downloader, device: Optional[int] = None, max_seqs: Optional[int] = None,
                max_tokens_per_seq: Optional[int] = None, max_batch_tokens: Optional[int] = None,
                page_tokens: Optional[int] = None, sample_mode: str = "reference",
-               speculate_next: Optional[bool] = None):
+               speculate_next: Optional[bool] = None, dtype: Optional[str] = None):
     self.shard = None
+    self.dtype = dtype or os.environ.get("XB_DTYPE", "bfloat16")   # "float32": hybrid models only (all-fp32 Linears)
     self.shard_downloader = shard_downloader
     self.stage: Optional[StageRuntime] = None
     self.tokenizer = None
@@ -202,7 +203,8 @@ class B200ShardInferenceEngine(InferenceEngine):
       if self.stage is not None:
         self.stage.close()
       st = StageRuntime(shard, self.model_config, device=self.device_index, max_batch_tokens=self.max_batch_tokens,
-                        max_seqs=self.max_seqs, max_tokens_per_seq=self.max_tokens_per_seq, page_tokens=self.page_tokens)
+                        max_seqs=self.max_seqs, max_tokens_per_seq=self.max_tokens_per_seq, page_tokens=self.page_tokens,
+                        dtype=self.dtype)
       st.load_dir(self.model_path)
       self.stage = st
       self._stage_changed()

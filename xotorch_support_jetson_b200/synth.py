@@ -76,6 +76,72 @@ def random_hf_state(cfg: dict, seed: int = 0, std: float = 0.02, norm_jitter: fl
   return out
 
 
+def refatar_param_shapes(cfg: dict) -> Dict[str, tuple]:
+  """Tensor names and shapes of a Refatar checkpoint for its ``config.json`` (Linear weights are [out, in])."""
+  D, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
+  taps = cfg["canon"]["taps"] if cfg.get("canon") else 0
+  sd = cfg["token_side"]["dim"] if cfg.get("token_side") else 0
+  sh = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+  if sd:
+    sh["side.embed"] = (V, sd * L)
+  for i, lc in enumerate(cfg["layers"]):
+    p, m = f"l{i}.", lc["mixer"]
+    sh[p + "norm1"] = sh[p + "norm1b"] = (D,)
+    if taps:
+      sh[p + "canon1"] = (D, taps)
+    if lc["type"] == "delta":
+      H, G, dk, dv, ct = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+      sh.update({p + "mix.q": (G * dk, D), p + "mix.q.conv": (G * dk, ct), p + "mix.k": (G * dk, D), p + "mix.k.conv": (G * dk, ct),
+                 p + "mix.v": (H * dv, D), p + "mix.v.conv": (H * dv, ct), p + "mix.b": (H, D), p + "mix.a": (H, D),
+                 p + "mix.A_log": (H,), p + "mix.dt_bias": (H,), p + "mix.norm": (dv,), p + "mix.g": (H * dv, D), p + "mix.o": (D, H * dv)})
+    else:
+      le, ri = m["left"], m["right"]
+      H, G, dk, dv = le["heads"], le["kv_heads"], le["dim"], le["vdim"]
+      Hr, rk, rv = ri["heads"], ri["dim"], ri["vdim"]
+      sh.update({p + "mix.left.q": (H * dk, D), p + "mix.left.q.b": (H * dk,), p + "mix.left.k": (G * dk, D), p + "mix.left.k.b": (G * dk,),
+                 p + "mix.left.v": (G * dv, D), p + "mix.left.v.b": (G * dv,), p + "mix.left.g": (H * dv, D), p + "mix.left.o": (D, H * dv),
+                 p + "mix.right.q": (Hr * rk, D), p + "mix.right.f": (Hr * rk, D), p + "mix.right.f.b": (Hr * rk,),
+                 p + "mix.right.lower": (Hr * rk,), p + "mix.right.v": (Hr * rv, D), p + "mix.right.norm": (rv,),
+                 p + "mix.right.o": (D, Hr * rv)})
+    if lc.get("mlp"):
+      F = lc["mlp"]["ff"]
+      sh.update({p + "norm2": (D,), p + "norm2b": (D,), p + "mlp.up": (F, D), p + "mlp.down": (D, F)})
+      if taps:
+        sh[p + "canon2"] = (D, taps)
+    if sd:
+      sh.update({p + "side.gate": (sd, D), p + "side.proj": (D, sd), p + "side.norm": (D,)})
+  return sh
+
+
+def random_refatar_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bfloat16, gain: float = 1.0,
+                         device: str = "cpu") -> Dict[str, torch.Tensor]:
+  """Seeded random Refatar weights: matrices N(0, gain^2 / in), offset-from-one norm weights N(0, 0.1^2), plain norm weights
+  1 + N(0, 0.1^2), filters N(0, 0.3^2), forget-gate floors in (0.05, 0.95), decay rates exp(A_log) in (0.5, 4)."""
+  out = {}
+  for idx, (name, shape) in enumerate(sorted(refatar_param_shapes(cfg).items())):
+    g = torch.Generator(device=device).manual_seed(seed * 1000003 + idx)
+    rn = lambda: torch.randn(shape, generator=g, device=device)  # noqa: E731
+    leaf = name.split(".")[-1]
+    if name.endswith("side.norm") or name.endswith("mix.norm") or name.endswith("right.norm"):
+      t = 1.0 + 0.1 * rn()
+    elif leaf in ("norm1", "norm1b", "norm2", "norm2b") or name == "final.norm":
+      t = 0.1 * rn()
+    elif leaf in ("canon1", "canon2", "conv"):
+      t = 0.3 * rn()
+    elif leaf == "lower":
+      t = 0.05 + 0.9 * torch.rand(shape, generator=g, device=device)
+    elif leaf == "A_log":
+      t = torch.log(0.5 + 3.5 * torch.rand(shape, generator=g, device=device))
+    elif leaf in ("dt_bias", "b") and len(shape) == 1:
+      t = 0.5 * rn()
+    elif name in ("embed", "side.embed"):
+      t = rn()
+    else:
+      t = gain * rn() / (shape[-1] ** 0.5)
+    out[name] = t.to(dtype)
+  return out
+
+
 def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0.02,
                             norm_jitter: float = 0.0, shard_bytes: int = 4 << 30,
                             peaked_head: float = 0.0) -> Path:
@@ -84,7 +150,10 @@ def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0
   path.mkdir(parents=True, exist_ok=True)
   with open(path / "config.json", "w") as f:
     json.dump(cfg, f, indent=1)
-  state = random_hf_state(cfg, seed=seed, std=std, norm_jitter=norm_jitter, peaked_head=peaked_head)
+  if cfg.get("architecture") == "Refatar":
+    state = random_refatar_state(cfg, seed=seed)
+  else:
+    state = random_hf_state(cfg, seed=seed, std=std, norm_jitter=norm_jitter, peaked_head=peaked_head)
   files, cur, cur_bytes = [], {}, 0
   for k, v in state.items():
     nb = v.numel() * v.element_size()
