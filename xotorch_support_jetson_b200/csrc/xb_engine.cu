@@ -41,6 +41,8 @@ struct xb_engine;
 struct HyModel;
 static void hy_destroy(HyModel* hy);
 static int hy_reserve(xb_engine* e);
+static int hy_finalize(xb_engine* e);
+static void hy_drop_plans(xb_engine* e);
 static int hy_missing(xb_engine* e, char* buf, size_t buflen, int* n_missing);
 static int hy_load_file(xb_engine* e, const char* path, const std::vector<StEntry>& entries, const uint8_t* data, size_t data_size,
                         int* n_tensors, uint64_t* n_bytes);
@@ -1071,6 +1073,7 @@ static int forward_impl(xb_engine* e, const xb_batch* b, void* out, void* const*
   cudaStream_t st = (cudaStream_t)stream;
   XB_CUDA(cudaSetDevice(e->device));
   XB_CHECK(e->n_slots > 0, "xb_kv_reserve must be called before xb_forward");
+  if (e->hy != nullptr) XB_TRY(hy_finalize(e));
   XB_CHECK(b->n_seqs > 0 && b->n_seqs <= d.max_seqs, "n_seqs %d out of range (max %d)", b->n_seqs, d.max_seqs);
   const bool first = shard_is_first(d), last = shard_is_last(d);
   XB_CHECK(first ? (b->tokens != nullptr) : (ho_in || b->hidden_in != nullptr),
@@ -1379,6 +1382,7 @@ extern "C" int xb_reserve_sms(xb_engine* e, int n) {
     if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   e->graphs.clear();     // captured steps and launch plans were sized for the old SM count
   e->plans.clear();
+  if (e->hy != nullptr) hy_drop_plans(e);
   e->reserved_sms = n;
   return 0;
 }

@@ -5,6 +5,7 @@
 #pragma once
 #include "xb_hybrid_kernels.cuh"
 #include <set>
+#include <tuple>
 
 struct HyTarget {
   void* dst = nullptr;
@@ -23,6 +24,8 @@ struct HyLayer {
   float *b_in = nullptr, *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *canon1 = nullptr,
         *canon2 = nullptr, *side_norm = nullptr, *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr, *head_norm = nullptr,
         *lower = nullptr;
+  // tile-major copies for the tcgen05 Linear (bf16 serving; made once all weights are in, see hy_finalize)
+  bf16 *t_in = nullptr, *t_o = nullptr, *t_o2 = nullptr, *t_up = nullptr, *t_down = nullptr, *t_sgate = nullptr, *t_sproj = nullptr;
   void *k_pool = nullptr, *v_pool = nullptr;
   size_t st_rec = 0, st_conv = 0, st_canon1 = 0, st_canon2 = 0;   // float offsets inside a slot's state
 };
@@ -42,10 +45,17 @@ struct HyModel {
   std::map<std::string, HyTarget> names;
   std::set<std::string> loaded;
   std::vector<void*> allocs;
+  bf16* t_head = nullptr;
+  bool finalized = false;
+  int use_tc = 1;            // XB_HY_TC=0: every Linear through the plain kernels (A/B)
+  size_t cap_P = 0, cap_m = 0, cap_head = 0;   // bytes of the Linear output buffers
+  std::map<std::tuple<const void*, const void*, const void*, int>, GemmPlan> plans;
 };
 
 static int* hy_rows_buffer(xb_engine* e) { return e->hy->d_rows; }
 static int hy_max_rows(xb_engine* e) { return e->hy->d.max_logit_rows > e->hy->d.max_seqs ? e->hy->d.max_logit_rows : e->hy->d.max_seqs; }
+
+static void hy_drop_plans(xb_engine* e) { e->hy->plans.clear(); }
 
 static int hy_alloc(HyModel* hy, void** p, size_t bytes) {
   XB_TRY(dmalloc(p, bytes));
@@ -70,7 +80,11 @@ static void hy_name_vec(HyModel* hy, const std::string& name, float* dst, long l
 static void hy_destroy(HyModel* hy) {
   if (hy == nullptr) return;
   for (void* p : hy->allocs) cudaFree(p);
-  for (HyLayer& l : hy->L) { cudaFree(l.k_pool); cudaFree(l.v_pool); }
+  for (HyLayer& l : hy->L) {
+    cudaFree(l.k_pool); cudaFree(l.v_pool);
+    cudaFree(l.t_in); cudaFree(l.t_o); cudaFree(l.t_o2); cudaFree(l.t_up); cudaFree(l.t_down); cudaFree(l.t_sgate); cudaFree(l.t_sproj);
+  }
+  cudaFree(hy->t_head);
   cudaFree(hy->state);
   delete hy;
 }
@@ -207,17 +221,25 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   const size_t R = (size_t)(d.max_logit_rows > d.max_seqs ? d.max_logit_rows : d.max_seqs);
   XB_TRY(hy_alloc_t(hy, &hy->x, Tm * D));
   XB_TRY(hy_alloc_t(hy, &hy->hn, Tm * D));
-  XB_TRY(hy_alloc_t(hy, &hy->P, Tm * hy->maxN));
+  const size_t ws_min = d.compute_fp32 ? 0 : ((size_t)32 << 20);   // room for the split-K planes of decode-sized batches
+  hy->cap_P = Tm * hy->maxN * 4 > ws_min ? Tm * hy->maxN * 4 : ws_min;
+  hy->cap_m = Tm * D * 4 > ws_min ? Tm * D * 4 : ws_min;
+  XB_TRY(hy_alloc(hy, (void**)&hy->P, hy->cap_P));
   XB_TRY(hy_alloc_t(hy, &hy->c, Tm * hy->maxC));
   XB_TRY(hy_alloc_t(hy, &hy->o, Tm * hy->maxO));
-  XB_TRY(hy_alloc_t(hy, &hy->m1, Tm * D));
-  XB_TRY(hy_alloc_t(hy, &hy->m2, Tm * D));
+  XB_TRY(hy_alloc(hy, (void**)&hy->m1, hy->cap_m));
+  XB_TRY(hy_alloc(hy, (void**)&hy->m2, hy->cap_m));
   XB_TRY(hy_alloc_t(hy, &hy->beta, Tm * hy->maxH));
   XB_TRY(hy_alloc_t(hy, &hy->decay, Tm * hy->maxH));
   XB_TRY(hy_alloc(hy, &hy->a1, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->a2, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->head_in, R * D * as));
-  XB_TRY(hy_alloc_t(hy, &hy->head_raw, R * (size_t)d.vocab));
+  hy->cap_head = R * (size_t)d.vocab * 4 > ws_min ? R * (size_t)d.vocab * 4 : ws_min;
+  XB_TRY(hy_alloc(hy, (void**)&hy->head_raw, hy->cap_head));
+  {
+    const char* g = getenv("XB_HY_TC");
+    if (g != nullptr && g[0] == '0') hy->use_tc = 0;
+  }
   XB_TRY(hy_alloc_t(hy, &hy->d_rows, R));
   XB_TRY(dmalloc((void**)&e->logits, R * (size_t)d.vocab * sizeof(float)));
   e->c.weight_bytes = wbytes;
@@ -256,6 +278,38 @@ static int hy_store(xb_engine* e, const std::string& name, const void* src, int 
   XB_CUDA(cudaDeviceSynchronize());
   if (staging) cudaFree(staging);
   hy->loaded.insert(name);
+  hy->finalized = false;
+  return 0;
+}
+
+// bf16 serving: once every tensor is in, each matrix the tcgen05 Linear can take (K a multiple of 8, at least one
+// 64-wide k block and 64 rows) gets its tile-major copy.  Runs before the first forward (never inside a capture).
+static int hy_tile(bf16** dst, const bf16* src, size_t rows, size_t K) {
+  if (*dst != nullptr || K % 8 != 0 || K < 64 || rows < 64) return 0;
+  XB_TRY(alloc_tiled(dst, rows, K));
+  return store_tiled(*dst, src, 0, rows, K);
+}
+static int hy_finalize(xb_engine* e) {
+  HyModel* hy = e->hy;
+  if (hy->finalized) return 0;
+  hy->finalized = true;
+  hy->plans.clear();
+  if (hy->d.compute_fp32 || !hy->use_tc || hy->loaded.size() < hy->names.size()) return 0;
+  const size_t D = hy->d.dim;
+  auto retile = [&](bf16** dst, const bf16* src, size_t rows, size_t K) -> int {
+    if (*dst != nullptr) { cudaFree(*dst); *dst = nullptr; }
+    return src != nullptr ? hy_tile(dst, src, rows, K) : 0;
+  };
+  for (HyLayer& l : hy->L) {
+    XB_TRY(retile(&l.t_in, l.w_in, l.n_in, D));
+    XB_TRY(retile(&l.t_o, l.w_o, D, l.n_o));
+    XB_TRY(retile(&l.t_o2, l.w_o2, D, l.n_o2));
+    XB_TRY(retile(&l.t_up, l.w_up, l.d.ff, D));
+    XB_TRY(retile(&l.t_down, l.w_down, D, l.d.ff));
+    XB_TRY(retile(&l.t_sgate, l.w_sgate, hy->d.side_dim, D));
+    XB_TRY(retile(&l.t_sproj, l.w_sproj, D, hy->d.side_dim));
+  }
+  XB_TRY(retile(&hy->t_head, hy->head, hy->d.vocab, D));
   return 0;
 }
 
@@ -334,15 +388,47 @@ static int hy_launch(xb_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block
 
 static LinOut hy_plain(const float* f, long long ld) {
   LinOut o;
-  o.f = f; o.h = nullptr; o.si = SplitInfo{0, 0, 0}; o.plane = 0; o.ld = ld;
+  o.f = f; o.h = nullptr; o.si = SplitInfo{0, 0, 0}; o.plane = 0; o.ld = ld; o.bias = nullptr;
   return o;
 }
 static LinOut hy_none() { return hy_plain(nullptr, 0); }
 
-// y[T, N] = x[T, K] w^T + bias into `out` (fp32, row pitch N)
+// The engine's tcgen05 Linear on a tile-major weight copy: decode-sized batches leave fp32 split-K planes, larger ones a
+// bf16 matrix; either way the consumer reads through LinOut (bias added on read).  false: not applicable here.
+static bool hy_tc_linear(xb_engine* e, const void* x, long long ldx, const bf16* wt, const float* bias, int T, int N, int K, void* out,
+                         size_t cap, cudaStream_t st, LinOut* y, int* rc) {
+  HyModel* hy = e->hy;
+  *rc = 0;
+  if (wt == nullptr || ldx % 8 != 0) return false;
+  const auto key = std::make_tuple((const void*)wt, x, (const void*)out, T);
+  auto it = hy->plans.find(key);
+  if (it == hy->plans.end()) {
+    GemmPlan p;
+    const int sms = (T <= 128 && e->reserved_sms > 0 && e->reserved_sms < e->num_sms) ? e->num_sms - e->reserved_sms : e->num_sms;
+    if ((*rc = xb_gemm_plan(&p, (const bf16*)x, ldx, wt, 1, T, N, K, out, N, nullptr, 0, sms, 0)) != 0) return true;
+    const size_t need = p.args.mode == XB_GEMM_SKINNY ? (size_t)p.split.splits * T * N * 4 : (size_t)T * N * 2;
+    if (need > cap) return false;
+    it = hy->plans.emplace(key, p).first;
+  }
+  const GemmPlan& p = it->second;
+  if ((*rc = run_gemm(e, p, st)) != 0) return true;
+  LAUNCH_COUNT(e);
+  LinOut o;
+  o.ld = N; o.bias = bias; o.plane = (long long)T * N;
+  if (p.args.mode == XB_GEMM_SKINNY) { o.f = (const float*)out; o.h = nullptr; o.si = p.split; }
+  else { o.f = nullptr; o.h = (const bf16*)out; o.si = SplitInfo{0, 0, 0}; }
+  *y = o;
+  return true;
+}
+
+// y[T, N] = x[T, K] w^T + bias into `out` (`cap` bytes).  wt: the weight's tile-major copy or nullptr.
 template <typename AT>
-static int hy_linear(xb_engine* e, const void* x, long long ldx, const bf16* w, const float* bias, int T, int N, int K, float* out,
-                     cudaStream_t st, LinOut* y) {
+static int hy_linear(xb_engine* e, const void* x, long long ldx, const bf16* w, const bf16* wt, const float* bias, int T, int N, int K,
+                     float* out, size_t cap, cudaStream_t st, LinOut* y) {
+  if (std::is_same<AT, bf16>::value) {
+    int rc = 0;
+    if (hy_tc_linear(e, x, ldx, wt, bias, T, N, K, out, cap, st, y, &rc)) return rc;
+  }
   const AT* xa = reinterpret_cast<const AT*>(x);
   if (T <= HY_SMALL_T)
     XB_TRY(hy_launch(e, hy_linear_small_kernel<AT>, dim3((N + 7) / 8), dim3(256), 0, st, xa, ldx, w, bias, out, (long long)N, T, N, K));
@@ -404,7 +490,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
     LinOut P, y1, y2 = hy_none();
     float s1 = 1.f, s2 = 0.f;
     XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, l.canon1, l.st_canon1, m, st));
-    XB_TRY(hy_linear<AT>(e, a1, D, l.w_in, l.b_in, T, l.n_in, D, hy->P, st, &P));
+    XB_TRY(hy_linear<AT>(e, a1, D, l.w_in, l.t_in, l.b_in, T, l.n_in, D, hy->P, hy->cap_P, st, &P));
     if (c.mixer == XB_MIX_DELTA) {
       const int H = c.d_heads, G = c.d_kv_heads, dk = c.d_dim, dv = c.d_vdim, tp = c.d_taps;
       float* tail = hy->state + l.st_conv;
@@ -418,7 +504,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
                        (const float*)hy->beta, (const float*)hy->decay, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, H, G, dk, dv));
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
                        (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv));
-      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, nullptr, T, D, l.n_o, hy->m1, st, &y1));
+      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     } else {
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
       const int Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
@@ -433,8 +519,8 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
                        hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, Hr, rk, rv));
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o2,
                        (const float*)l.head_norm, P, -1, d.norm_eps, 1.0f, a2, (long long)l.n_o2, Hr, rv));
-      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, nullptr, T, D, l.n_o, hy->m1, st, &y1));
-      XB_TRY(hy_linear<AT>(e, a2, l.n_o2, l.w_o2, nullptr, T, D, l.n_o2, hy->m2, st, &y2));
+      XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
+      XB_TRY(hy_linear<AT>(e, a2, l.n_o2, l.w_o2, l.t_o2, nullptr, T, D, l.n_o2, hy->m2, hy->cap_m, st, &y2));
       s1 = c.left_scale;
       s2 = c.right_scale;
     }
@@ -444,20 +530,20 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
     if (has_ff) {
       LinOut u, dn;
       XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, l.canon2, l.st_canon2, m, st));
-      XB_TRY(hy_linear<AT>(e, a1, D, l.w_up, nullptr, T, c.ff, D, hy->P, st, &u));
+      XB_TRY(hy_linear<AT>(e, a1, D, l.w_up, l.t_up, nullptr, T, c.ff, D, hy->P, hy->cap_P, st, &u));
       const long long n = (long long)T * c.ff;
       XB_TRY(hy_launch(e, hy_relu2_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, u, a1, (long long)c.ff, T, c.ff));
-      XB_TRY(hy_linear<AT>(e, a1, c.ff, l.w_down, nullptr, T, D, c.ff, hy->m1, st, &dn));
+      XB_TRY(hy_linear<AT>(e, a1, c.ff, l.w_down, l.t_down, nullptr, T, D, c.ff, hy->m1, hy->cap_m, st, &dn));
       XB_TRY(hy_row_op<AT>(e, T, dn, 1.f, hy_none(), 0.f, l.norm2b, 1.f, has_side ? nullptr : next_norm, has_side ? (void*)a1 : nullptr, st));
     }
     if (has_side) {
       LinOut gt, yy;
       const int sd = d.side_dim;
-      XB_TRY(hy_linear<AT>(e, a1, D, l.w_sgate, nullptr, T, sd, D, hy->P, st, &gt));
+      XB_TRY(hy_linear<AT>(e, a1, D, l.w_sgate, l.t_sgate, nullptr, T, sd, D, hy->P, hy->cap_P, st, &gt));
       const long long n = (long long)T * sd;
       XB_TRY(hy_launch(e, hy_side_gate_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, gt, (const int*)e->in_tokens,
                        (const bf16*)hy->side_embed, (long long)sd * d.n_layers, li * sd, d.vocab, a2, (long long)sd, T, sd));
-      XB_TRY(hy_linear<AT>(e, a2, sd, l.w_sproj, nullptr, T, D, sd, hy->m1, st, &yy));
+      XB_TRY(hy_linear<AT>(e, a2, sd, l.w_sproj, l.t_sproj, nullptr, T, D, sd, hy->m1, hy->cap_m, st, &yy));
       XB_TRY(hy_row_op<AT>(e, T, yy, 1.f, hy_none(), 0.f, l.side_norm, 0.f, next_norm, nullptr, st));
     }
     if (taps != nullptr && taps[li] != nullptr)
@@ -469,7 +555,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
       const int* idx = e->sel_rows != nullptr ? hy->d_rows : m.seq_last;
       LinOut y;
       XB_TRY(hy_launch(e, hy_gather_rows_kernel<AT>, dim3(n), dim3(256), 0, st, (const float*)hy->hn, idx, reinterpret_cast<AT*>(hy->head_in), D));
-      XB_TRY(hy_linear<AT>(e, hy->head_in, D, hy->head, nullptr, n, d.vocab, D, hy->head_raw, st, &y));
+      XB_TRY(hy_linear<AT>(e, hy->head_in, D, hy->head, hy->t_head, nullptr, n, d.vocab, D, hy->head_raw, hy->cap_head, st, &y));
       const long long tot = (long long)n * d.vocab;
       XB_TRY(hy_launch(e, hy_logits_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, st, y, d.logit_softcap, e->logits, n, d.vocab));
     }

@@ -23,16 +23,18 @@ struct LinOut {
   SplitInfo si;        // si.splits == 0: one plane
   long long plane;     // floats between planes
   long long ld;
+  const float* bias;   // added on read (outputs of the tcgen05 Linear; the plain kernels add it themselves), or nullptr
 };
 
 __device__ __forceinline__ float lin_at(const LinOut& o, long long row, int col) {
-  if (o.h != nullptr) return bf2f(o.h[row * o.ld + col]);
+  const float b = o.bias != nullptr ? o.bias[col] : 0.f;
+  if (o.h != nullptr) return bf2f(o.h[row * o.ld + col]) + b;
   const float* p = o.f + row * o.ld + col;
-  if (o.si.splits == 0) return *p;
+  if (o.si.splits == 0) return *p + b;
   const int n = xb_n_segments(o.si, col);
   float s = 0.f;
   for (int i = 0; i < n; ++i) s += p[i * o.plane];
-  return s;
+  return s + b;
 }
 
 template <typename AT> __device__ __forceinline__ void act_store(AT* p, float v);
