@@ -685,6 +685,102 @@ def e2e_engine_api(runner, cfg, prompt, K, W):
                                  "device, ids streamed to a pinned table, reference-semantics sampler (top-k 35, q noise) every step"}}
 
 
+def run_family_compare(args):
+  """--compare-families: prefill and decode throughput of a hybrid (Refatar) model beside the Llama-shaped model of the
+  same width, depth and vocabulary, both with random weights made on the GPU, through StageRuntime (the serving path's
+  native calls).  One JSON line per (model, leg, size).  Timing: CUDA events on the launching stream, W warm-up
+  iterations, synchronize on both sides; inputs + weights exceed L2 (2.5 GB of weights are streamed per step)."""
+  import torch
+  import __graft_entry__ as graft
+  graft.build()
+  from xotorch_support_jetson_b200 import model_config as mc
+  from xotorch_support_jetson_b200.models import model_cards
+  from xotorch_support_jetson_b200.pipeline import gpu_random_getter
+  from xotorch_support_jetson_b200.shard import Shard
+  from xotorch_support_jetson_b200.stage import StageRuntime
+  from xotorch_support_jetson_b200.synth import random_refatar_state
+  torch.cuda.set_device(0)
+  dev = torch.device("cuda", 0)
+  peaks = measured_peaks()
+  K, W = args.steps, max(3, args.warmup)
+  prefill_sizes = [int(x) for x in args.compare_prefill.split(",")]
+  decode_batches = [int(x) for x in args.compare_decode.split(",")]
+  ctx = args.prompt_len
+  stream = torch.cuda.Stream(device=dev)
+  for mid in args.compare_models.split(","):
+    raw = model_cards[mid]["hf_config"]
+    with tempfile.TemporaryDirectory() as td:
+      (Path(td) / "config.json").write_text(json.dumps(raw))
+      cfg = mc.load_model_config(Path(td) / "config.json")
+    nl = cfg["num_layers"]
+    max_seqs = max(decode_batches + [1])
+    cap = max(prefill_sizes + [2048])
+    st = StageRuntime(Shard(mid, 0, nl - 1, nl), cfg, device=0, max_batch_tokens=cap, max_seqs=max_seqs,
+                      max_tokens_per_seq=max(ctx + 2 * (K + W) + 64, cap), page_tokens=64)
+    if mc.is_hybrid(cfg):
+      st.load_state(random_refatar_state(raw, seed=0, device="cuda"))
+    else:
+      get, has = gpu_random_getter(raw, 0, 0.02, dev)
+      st.load_hf_tensors(get, has)
+    V = cfg["vocab_size"]
+    g = torch.Generator(device=dev).manual_seed(1)
+    wbytes = st.counters()["weight_bytes"]
+
+    def timed(fn, n):
+      torch.cuda.synchronize()
+      e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      e0.record(stream)
+      for _ in range(n):
+        fn()
+      e1.record(stream)
+      torch.cuda.synchronize()
+      return e0.elapsed_time(e1) / n
+
+    with torch.cuda.stream(stream):
+      for T in prefill_sizes:
+        ids = torch.randint(1, V, (T,), generator=g, device=dev, dtype=torch.int32)
+
+        def prefill():
+          st.forward([0], [T], [0], tokens=ids)     # position 0: a fresh sequence every time (state and cache rewritten)
+        for _ in range(W):
+          prefill()
+        ms = timed(prefill, max(3, K // 8))
+        st.release_slot(0)
+        print(json.dumps({"compare": "prefill", "model": mid, "tokens": T, "ms": round(ms, 4), "tok_s": round(T / ms * 1e3, 1),
+                          "dtype": "bf16", "data": "synthetic", "peaks": peaks["source"]}), flush=True)
+      for B in decode_batches:
+        slots = list(range(B))
+        # context: ctx tokens per sequence, prefilled in chunks
+        for b in range(B):
+          for c0 in range(0, ctx, cap):
+            n = min(cap, ctx - c0)
+            st.forward([b], [n], [c0], tokens=torch.randint(1, V, (n,), generator=g, device=dev, dtype=torch.int32))
+        pos = [ctx] * B
+        tok = torch.randint(1, V, (B,), generator=g, device=dev, dtype=torch.int32)
+        l0 = None
+
+        def step():
+          nonlocal tok
+          logits = st.forward(slots, [1] * B, pos, tokens=tok)
+          tok = st.sample(logits, temp=0.0)
+          for i in range(B):
+            pos[i] += 1
+        for _ in range(W):
+          step()
+        l0 = st.counters()["launches"]
+        ms = timed(step, K)
+        launches = (st.counters()["launches"] - l0) // K
+        for b in range(B):
+          st.release_slot(b)
+        print(json.dumps({"compare": "decode", "model": mid, "batch": B, "context": ctx, "ms_per_step": round(ms, 4),
+                          "tok_s": round(B / ms * 1e3, 1), "launches_per_step": int(launches),
+                          "weight_stream_frac_of_hbm": round(wbytes / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3),
+                          "dtype": "bf16", "data": "synthetic", "peaks": peaks["source"]}), flush=True)
+    st.close()
+    del st
+    torch.cuda.empty_cache()
+
+
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
@@ -701,7 +797,14 @@ def main():
                   help="micro-batches in flight (default: one per GPU)")
   ap.add_argument("--reps", type=int, default=5, help="the K-step timed region is repeated this often; the median is reported")
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--compare-families", action="store_true",
+                  help="instead of the headline workload: prefill / decode throughput of a hybrid model beside the Llama-shaped one of equal size")
+  ap.add_argument("--compare-models", default="refatar-1b,llama-3.2-1b")
+  ap.add_argument("--compare-prefill", default="512,2048,4096", help="prompt lengths (tokens of one sequence per call)")
+  ap.add_argument("--compare-decode", default="1,8,32", help="decode batch sizes at context --prompt-len")
   args = ap.parse_args()
+  if args.compare_families:
+    return run_family_compare(args)
   if args.warmup < 3 and args.impl == "b200":
     args.warmup = 3
   if args.impl == "reference":

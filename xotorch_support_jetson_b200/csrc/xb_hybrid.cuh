@@ -283,9 +283,9 @@ static int hy_store(xb_engine* e, const std::string& name, const void* src, int 
 }
 
 // bf16 serving: once every tensor is in, each matrix the tcgen05 Linear can take (K a multiple of 8, at least one
-// 64-wide k block and 64 rows) gets its tile-major copy.  Runs before the first forward (never inside a capture).
+// 64-wide k block and 16 rows) gets its tile-major copy.  Runs before the first forward (never inside a capture).
 static int hy_tile(bf16** dst, const bf16* src, size_t rows, size_t K) {
-  if (*dst != nullptr || K % 8 != 0 || K < 64 || rows < 64) return 0;
+  if (*dst != nullptr || K % 8 != 0 || K < 64 || rows < 16) return 0;
   XB_TRY(alloc_tiled(dst, rows, K));
   return store_tiled(*dst, src, 0, rows, K);
 }
@@ -446,6 +446,8 @@ static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float 
   RowOpArgs a;
   a.x = hy->x; a.m1 = m1; a.m2 = m2; a.s1 = s1; a.s2 = s2; a.bw = bw; a.bw_one = bw_one; a.nw = nw; a.hn = hy->hn; a.xa = xa;
   a.eps = hy->d.norm_eps; a.D = hy->d.dim;
+  if (T <= 64 && hy->d.dim >= 1024)   // decode-sized batches: few rows, so more threads per row keep more loads in flight
+    return hy_launch(e, hy_row_op_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)hy->d.dim * sizeof(float), st, a);
   return hy_launch(e, hy_row_op_kernel<AT, 256>, dim3(T), dim3(256), (size_t)hy->d.dim * sizeof(float), st, a);
 }
 
@@ -500,24 +502,30 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
         XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (l.c_conv + 255) / 256), dim3(256), 0, st, P, 0, l.c_conv, tp, tail, SS, m));
       XB_TRY(hy_launch(e, hy_delta_prep_kernel, dim3(T), dim3(256), 0, st, hy->c, (long long)l.c_conv, P, l.off_b, l.off_a,
                        (const float*)l.A_log, (const float*)l.dt_bias, hy->beta, hy->decay, H, G, dk));
-      XB_TRY(hy_launch(e, hy_delta_rule_kernel, dim3(n_seqs, H, (dv + 7) / 8), dim3(256), 0, st, (const float*)hy->c, (long long)l.c_conv,
+      XB_TRY(hy_launch(e, hy_delta_rule_kernel, dim3(n_seqs, H, (dv + 7) / 8), dim3(256), (size_t)HY_TS * (2 * dk + 10) * sizeof(float), st, (const float*)hy->c, (long long)l.c_conv,
                        (const float*)hy->beta, (const float*)hy->decay, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, H, G, dk, dv));
-      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
+      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (H + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
                        (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     } else {
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
       const int Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
-      XB_TRY(hy_launch(e, hy_kv_append_kernel<KT>, dim3(T), dim3(256), 0, st, P, l.off_k, l.off_v, (KT*)l.k_pool, (KT*)l.v_pool, m, G, dk, dv));
-      XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT>, dim3(T, (H + 3) / 4), dim3(128), (size_t)4 * dk * sizeof(float), st, P, l.off_q,
-                       l.off_g, (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f,
-                       a1, (long long)l.n_o));
+      XB_TRY(hy_launch(e, hy_kv_append_kernel<KT>, dim3(T, (G * (dk + dv) + 255) / 256), dim3(256), 0, st, P, l.off_k, l.off_v, (KT*)l.k_pool, (KT*)l.v_pool, m, G, dk, dv));
+      {
+        // warps per (token, head): one per 64 visible keys, at most 8
+        int aw = (c.a_window + c.a_keep_first + 63) / 64;
+        aw = aw < 1 ? 1 : (aw > 8 ? 8 : aw);
+        const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dv)) * sizeof(float);
+        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT>, dim3(T, H), dim3(32 * aw), asm_bytes, st, P, l.off_q, l.off_g,
+                         (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f, a1,
+                         (long long)l.n_o));
+      }
       const long long ldc = 2LL * Hr * rk + (long long)Hr * rv;
-      XB_TRY(hy_launch(e, hy_hgrn_prep_kernel, dim3(T), dim3(256), 0, st, P, l.off_rq, l.off_rf, l.off_rv, (const float*)l.lower, hy->c,
+      XB_TRY(hy_launch(e, hy_hgrn_prep_kernel, dim3(T, (2 * Hr * rk + Hr * rv + 255) / 256), dim3(256), 0, st, P, l.off_rq, l.off_rf, l.off_rv, (const float*)l.lower, hy->c,
                        ldc, Hr * rk, Hr * rv));
-      XB_TRY(hy_launch(e, hy_hgrn_kernel, dim3(n_seqs, Hr, (rv + 7) / 8), dim3(256), 0, st, (const float*)hy->c, ldc,
+      XB_TRY(hy_launch(e, hy_hgrn_kernel, dim3(n_seqs, Hr, (rv + 7) / 8), dim3(256), (size_t)HY_TS * (2 * rk + 8) * sizeof(float), st, (const float*)hy->c, ldc,
                        hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, Hr, rk, rv));
-      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o2,
+      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (Hr + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o2,
                        (const float*)l.head_norm, P, -1, d.norm_eps, 1.0f, a2, (long long)l.n_o2, Hr, rv));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
       XB_TRY(hy_linear<AT>(e, a2, l.n_o2, l.w_o2, l.t_o2, nullptr, T, D, l.n_o2, hy->m2, hy->cap_m, st, &y2));

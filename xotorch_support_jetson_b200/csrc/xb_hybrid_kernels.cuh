@@ -316,114 +316,157 @@ __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ 
 //   S_j <- g S_j;  u_j = beta (v_j - k . S_j);  S_j <- S_j + k u_j;  o_j = q . S_j
 // so a warp owns one column (lane l holds rows l, l+32, ...), and with a = k . S_j, b = q . S_j, qk = q . k taken on
 // the OLD column in one reduction: u_j = beta (v_j - g a), o_j = g b + qk u_j.
-// grid (n_seqs, H, ceil(dv / warps)); state [slot][H][dv][dk] fp32.
+// The warps of a block share (sequence, head): the inputs of HY_TS steps (q, k, the block's v columns, beta, decay) are
+// staged in shared memory with coalesced loads, then every warp walks the steps from there.
+// grid (n_seqs, H, ceil(dv / warps)); state [slot][H][dv][dk] fp32; dynamic smem HY_TS * (2 dk + warps + 2) floats.
+#define HY_TS 16
 __global__ void __launch_bounds__(256) hy_delta_rule_kernel(const float* __restrict__ c, long long ldc, const float* __restrict__ beta,
                                                             const float* __restrict__ decay, float* __restrict__ state,
                                                             long long state_stride, float* __restrict__ o, long long ldo, BatchMeta m,
                                                             int H, int G, int dk, int dv) {
+  extern __shared__ float stg[];
   const int s = blockIdx.x, h = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.z * (blockDim.x >> 5) + warp;
-  if (j >= dv) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int j0 = blockIdx.z * nw, j = j0 + warp;
+  const bool live = j < dv;
   const SeqSpan sp = seq_span(m, s);
   const int g = h / (H / G);
-  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + j) * dk;
+  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + (live ? j : 0)) * dk;
   float S[HY_MAX_KREG];
 #pragma unroll
   for (int i = 0; i < HY_MAX_KREG; ++i) {
     const int r = lane + 32 * i;
-    S[i] = (sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
+    S[i] = (live && sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
   }
-  const long long qoff = (long long)g * dk, koff = (long long)(G + g) * dk, voff = (long long)2 * G * dk + (long long)h * dv + j;
-  for (int t = 0; t < sp.len; ++t) {
-    const long long row = sp.start + t;
-    const float* cr = c + row * ldc;
-    float qv[HY_MAX_KREG], kv[HY_MAX_KREG];
-    float a = 0.f, b = 0.f, qk = 0.f;
+  const long long qoff = (long long)g * dk, koff = (long long)(G + g) * dk, voff = (long long)2 * G * dk + (long long)h * dv + j0;
+  const int stride = 2 * dk + nw + 2;
+  for (int t0 = 0; t0 < sp.len; t0 += HY_TS) {
+    const int nt = sp.len - t0 < HY_TS ? sp.len - t0 : HY_TS;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * stride; idx += blockDim.x) {
+      const int ts = idx / stride, cc = idx - ts * stride;
+      const long long row = sp.start + t0 + ts;
+      const float* cr = c + row * ldc;
+      float v;
+      if (cc < dk) v = cr[qoff + cc];
+      else if (cc < 2 * dk) v = cr[koff + cc - dk];
+      else if (cc < 2 * dk + nw) v = (j0 + cc - 2 * dk < dv) ? cr[voff + cc - 2 * dk] : 0.f;
+      else if (cc == 2 * dk + nw) v = beta[row * H + h];
+      else v = decay[row * H + h];
+      stg[idx] = v;
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int ts = 0; ts < nt; ++ts) {
+      const float* sr = stg + ts * stride;
+      float kv[HY_MAX_KREG];
+      float a = 0.f, b = 0.f, qk = 0.f;
+#pragma unroll
+      for (int i = 0; i < HY_MAX_KREG; ++i) {
+        const int r = lane + 32 * i;
+        const float qv = r < dk ? sr[r] : 0.f;
+        kv[i] = r < dk ? sr[dk + r] : 0.f;
+        a = fmaf(kv[i], S[i], a);
+        b = fmaf(qv, S[i], b);
+        qk = fmaf(qv, kv[i], qk);
+      }
+      const float v = sr[2 * dk + warp], be = sr[2 * dk + nw], gd = sr[2 * dk + nw + 1];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+        qk += __shfl_xor_sync(0xffffffffu, qk, off);
+      }
+      const float u = be * (v - gd * a);
+#pragma unroll
+      for (int i = 0; i < HY_MAX_KREG; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
+      if (lane == 0) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = fmaf(qk, u, gd * b);
+    }
+  }
+  if (live) {
 #pragma unroll
     for (int i = 0; i < HY_MAX_KREG; ++i) {
       const int r = lane + 32 * i;
-      qv[i] = r < dk ? cr[qoff + r] : 0.f;
-      kv[i] = r < dk ? cr[koff + r] : 0.f;
-      a = fmaf(kv[i], S[i], a);
-      b = fmaf(qv[i], S[i], b);
-      qk = fmaf(qv[i], kv[i], qk);
+      if (r < dk) st[r] = S[i];
     }
-    const float v = cr[voff], be = beta[row * H + h], gd = decay[row * H + h];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      a += __shfl_xor_sync(0xffffffffu, a, off);
-      b += __shfl_xor_sync(0xffffffffu, b, off);
-      qk += __shfl_xor_sync(0xffffffffu, qk, off);
-    }
-    const float u = be * (v - gd * a);
-#pragma unroll
-    for (int i = 0; i < HY_MAX_KREG; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
-    if (lane == 0) o[row * ldo + (long long)h * dv + j] = fmaf(qk, u, gd * b);
-  }
-#pragma unroll
-  for (int i = 0; i < HY_MAX_KREG; ++i) {
-    const int r = lane + 32 * i;
-    if (r < dk) st[r] = S[i];
   }
 }
 
 // ----------------------------------------------------------------------------- HGRN2
-// Prep: q = silu(.), f = lower + (1 - lower) sigmoid(.), v copied, into one fp32 row [q | f | v].
+// Prep: q = silu(.), f = lower + (1 - lower) sigmoid(.), v copied, into one fp32 row [q | f | v].  grid (T, ceil(n / 256)).
 __global__ void hy_hgrn_prep_kernel(LinOut P, int off_q, int off_f, int off_v, const float* __restrict__ lower, float* __restrict__ c,
                                     long long ldc, int HK, int HV) {
   const long long t = blockIdx.x;
-  float* row = c + t * ldc;
-  for (int i = threadIdx.x; i < 2 * HK + HV; i += blockDim.x) {
-    float v;
-    if (i < HK) v = hy_silu(lin_at(P, t, off_q + i));
-    else if (i < 2 * HK) {
-      const float lo = lower[i - HK];
-      v = lo + (1.0f - lo) * hy_sigmoid(lin_at(P, t, off_f + i - HK));
-    } else v = lin_at(P, t, off_v + i - 2 * HK);
-    row[i] = v;
-  }
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= 2 * HK + HV) return;
+  float v;
+  if (i < HK) v = hy_silu(lin_at(P, t, off_q + i));
+  else if (i < 2 * HK) {
+    const float lo = lower[i - HK];
+    v = lo + (1.0f - lo) * hy_sigmoid(lin_at(P, t, off_f + i - HK));
+  } else v = lin_at(P, t, off_v + i - 2 * HK);
+  c[t * ldc + i] = v;
 }
 
 // Recurrence per head: S <- diag(f) S + (1 - f) v^T, o = S^T q.  Column j: S_j <- f * S_j + (1 - f) v_j, o_j = q . S_j.
+// Same layout as the delta rule: a warp per value column, inputs of HY_TS steps staged in shared memory.
+// dynamic smem HY_TS * (2 dk + warps) floats.
 __global__ void __launch_bounds__(256) hy_hgrn_kernel(const float* __restrict__ c, long long ldc, float* __restrict__ state,
                                                       long long state_stride, float* __restrict__ o, long long ldo, BatchMeta m, int H,
                                                       int dk, int dv) {
+  extern __shared__ float stg[];
   const int s = blockIdx.x, h = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.z * (blockDim.x >> 5) + warp;
-  if (j >= dv) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int j0 = blockIdx.z * nw, j = j0 + warp;
+  const bool live = j < dv;
   const SeqSpan sp = seq_span(m, s);
-  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + j) * dk;
+  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + (live ? j : 0)) * dk;
   float S[HY_MAX_KREG];
 #pragma unroll
   for (int i = 0; i < HY_MAX_KREG; ++i) {
     const int r = lane + 32 * i;
-    S[i] = (sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
+    S[i] = (live && sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
   }
   const long long HK = (long long)H * dk;
-  const long long qoff = (long long)h * dk, foff = HK + (long long)h * dk, voff = 2 * HK + (long long)h * dv + j;
-  for (int t = 0; t < sp.len; ++t) {
-    const long long row = sp.start + t;
-    const float* cr = c + row * ldc;
-    const float v = cr[voff];
-    float acc = 0.f;
+  const long long qoff = (long long)h * dk, foff = HK + (long long)h * dk, voff = 2 * HK + (long long)h * dv + j0;
+  const int stride = 2 * dk + nw;
+  for (int t0 = 0; t0 < sp.len; t0 += HY_TS) {
+    const int nt = sp.len - t0 < HY_TS ? sp.len - t0 : HY_TS;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * stride; idx += blockDim.x) {
+      const int ts = idx / stride, cc = idx - ts * stride;
+      const float* cr = c + (long long)(sp.start + t0 + ts) * ldc;
+      float v;
+      if (cc < dk) v = cr[qoff + cc];
+      else if (cc < 2 * dk) v = cr[foff + cc - dk];
+      else v = (j0 + cc - 2 * dk < dv) ? cr[voff + cc - 2 * dk] : 0.f;
+      stg[idx] = v;
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int ts = 0; ts < nt; ++ts) {
+      const float* sr = stg + ts * stride;
+      const float v = sr[2 * dk + warp];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < HY_MAX_KREG; ++i) {
+        const int r = lane + 32 * i;
+        if (r < dk) {
+          const float f = sr[dk + r];
+          S[i] = fmaf(f, S[i], (1.0f - f) * v);
+          acc = fmaf(sr[r], S[i], acc);
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = acc;
+    }
+  }
+  if (live) {
 #pragma unroll
     for (int i = 0; i < HY_MAX_KREG; ++i) {
       const int r = lane + 32 * i;
-      if (r < dk) {
-        const float f = cr[foff + r];
-        S[i] = fmaf(f, S[i], (1.0f - f) * v);
-        acc = fmaf(cr[qoff + r], S[i], acc);
-      }
+      if (r < dk) st[r] = S[i];
     }
-    acc = warp_sum(acc);
-    if (lane == 0) o[row * ldo + (long long)h * dv + j] = acc;
-  }
-#pragma unroll
-  for (int i = 0; i < HY_MAX_KREG; ++i) {
-    const int r = lane + 32 * i;
-    if (r < dk) st[r] = S[i];
   }
 }
 
@@ -435,7 +478,7 @@ __global__ void __launch_bounds__(256) hy_head_norm_kernel(const float* __restri
                                                            long long ld_out, int H, int dv) {
   const long long t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int h = warp; h < H; h += nw) {
+  for (int h = blockIdx.y * nw + warp; h < H; h += nw * gridDim.y) {
     const float* p = o + t * ldo + (long long)h * dv;
     float ss = 0.f;
     for (int j = lane; j < dv; j += 32) ss += p[j] * p[j];
@@ -458,7 +501,7 @@ __global__ void hy_kv_append_kernel(LinOut P, int off_k, int off_v, KT* __restri
   const int s = m.tok_seq[row], pos = m.tok_pos[row];
   const int page = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
   const int in_page = pos % m.page_tokens;
-  for (int i = threadIdx.x; i < G * (dk + dv); i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < G * (dk + dv); i += blockDim.x * gridDim.y) {
     if (i < G * dk) {
       const int g = i / dk, d = i - g * dk;
       act_store<KT>(k_pool + (((long long)page * G + g) * m.page_tokens + in_page) * dk + d, lin_at(P, row, off_k + i));
@@ -470,24 +513,55 @@ __global__ void hy_kv_append_kernel(LinOut P, int off_k, int off_v, KT* __restri
   }
 }
 
-// One warp per (token, query head).  Query i sees key j when j <= i and (i - j < window or j < keep_first): the kept
-// first keys, then the window, 32 keys at a time: a lane scores one key (fp32 dot with the query in shared memory),
-// the warp does the online softmax, then lanes own value channels for the weighted sum.  No rotation: positions
-// enter through the mask only.  The epilogue multiplies by sigmoid(gate column) and `out_scale`.
-// dv <= 256.  Dynamic shared memory: warps * dk floats.
+// q . k for one key row; 16-byte loads when the row length allows (rows then start on 16-byte boundaries)
+template <typename KT> __device__ __forceinline__ float hy_dot_row(const float* __restrict__ q, const KT* __restrict__ kr, int dk);
+template <> __device__ __forceinline__ float hy_dot_row<float>(const float* __restrict__ q, const float* __restrict__ kr, int dk) {
+  float d = 0.f;
+  if ((dk & 3) == 0) {
+    for (int i = 0; i < dk; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+      const float4 q4 = *reinterpret_cast<const float4*>(q + i);
+      d = fmaf(q4.x, k4.x, d); d = fmaf(q4.y, k4.y, d); d = fmaf(q4.z, k4.z, d); d = fmaf(q4.w, k4.w, d);
+    }
+  } else {
+    for (int i = 0; i < dk; ++i) d = fmaf(q[i], kr[i], d);
+  }
+  return d;
+}
+template <> __device__ __forceinline__ float hy_dot_row<bf16>(const float* __restrict__ q, const bf16* __restrict__ kr, int dk) {
+  float d = 0.f;
+  if ((dk & 7) == 0) {
+    for (int i = 0; i < dk; i += 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(kr + i);
+      const float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), e = bf2_to_f2(u.w);
+      const float4 q0 = *reinterpret_cast<const float4*>(q + i), q1 = *reinterpret_cast<const float4*>(q + i + 4);
+      d = fmaf(q0.x, a.x, d); d = fmaf(q0.y, a.y, d); d = fmaf(q0.z, b.x, d); d = fmaf(q0.w, b.y, d);
+      d = fmaf(q1.x, c.x, d); d = fmaf(q1.y, c.y, d); d = fmaf(q1.z, e.x, d); d = fmaf(q1.w, e.y, d);
+    }
+  } else {
+    for (int i = 0; i < dk; ++i) d = fmaf(q[i], bf2f(kr[i]), d);
+  }
+  return d;
+}
+
+// One block per (token, query head); its warps split the visible keys 32 at a time.  Query i sees key j when j <= i and
+// (i - j < window or j < keep_first): the kept first keys, then the window.  In a 32-key tile a lane scores one key (fp32
+// dot with the query in shared memory), the warp does the online softmax, then lanes own value channels for the weighted
+// sum; at the end warp 0 merges the warps' (max, sum, accumulator) triples.  No rotation: positions enter through the
+// mask only.  The epilogue multiplies by sigmoid(gate column) and `out_scale`.
+// dv <= 256.  Dynamic shared memory: (dk rounded up to 4) + warps * (2 + dv) floats.
 template <typename KT, typename AT>
-__global__ void __launch_bounds__(128) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
+__global__ void __launch_bounds__(256) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
                                                              const KT* __restrict__ v_pool, BatchMeta m, int H, int G, int dk, int dv,
                                                              int window, int keep_first, float scale, float out_scale,
                                                              AT* __restrict__ out, long long ld_out) {
-  extern __shared__ float qsm[];
-  const int row = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y * (blockDim.x >> 5) + warp;
-  if (h >= H) return;
-  float* q = qsm + warp * dk;
-  for (int i = lane; i < dk; i += 32) q[i] = lin_at(P, row, off_q + h * dk + i) * scale;
-  __syncwarp();
+  extern __shared__ __align__(16) float qsm[];
+  const int row = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float* q = qsm;
+  float* part = qsm + ((dk + 3) & ~3);   // per warp: max, sum, acc[dv]
+  for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = lin_at(P, row, off_q + h * dk + i) * scale;
+  __syncthreads();
   const int g = h / (H / G);
   const int s = m.tok_seq[row], pos = m.tok_pos[row];
   const int* pages = m.page_table + (long long)m.seq_slot[s] * m.max_pages;
@@ -498,17 +572,14 @@ __global__ void __launch_bounds__(128) hy_attn_window_kernel(LinOut P, int off_q
   float acc[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-  for (int base = 0; base < n_vis; base += 32) {
+  for (int base = warp * 32; base < n_vis; base += nw * 32) {
     const int idx = base + lane;
     float sc = -INFINITY;
     long long prow = 0;
     if (idx < n_vis) {
       const int kp = idx < n_first ? idx : lo + (idx - n_first);
       prow = ((long long)pages[kp / m.page_tokens] * G + g) * m.page_tokens + kp % m.page_tokens;
-      const KT* kr = k_pool + prow * dk;
-      float d = 0.f;
-      for (int i = 0; i < dk; ++i) d = fmaf(q[i], act_load<KT>(kr + i), d);
-      sc = d;
+      sc = hy_dot_row<KT>(q, k_pool + prow * dk, dk);
     }
     const float tmax = warp_max(sc);
     const float nm = fmaxf(mx, tmax);
@@ -530,7 +601,31 @@ __global__ void __launch_bounds__(128) hy_attn_window_kernel(LinOut P, int off_q
       }
     }
   }
-  const float inv = out_scale / l;
+  float* mine = part + (long long)warp * (2 + dv);
+  if (lane == 0) { mine[0] = mx; mine[1] = l; }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int d = lane + 32 * c;
+    if (d < dv) mine[2 + d] = acc[c];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float M = -INFINITY;
+  for (int w = 0; w < nw; ++w) M = fmaxf(M, part[(long long)w * (2 + dv)]);
+  float L = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  for (int w = 0; w < nw; ++w) {
+    const float* pw = part + (long long)w * (2 + dv);
+    const float f = expf(pw[0] - M);     // a warp without keys holds max = -inf: weight 0
+    L += pw[1] * f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv) acc[c] = fmaf(pw[2 + d], f, acc[c]);
+    }
+  }
+  const float inv = out_scale / L;
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     const int d = lane + 32 * c;
