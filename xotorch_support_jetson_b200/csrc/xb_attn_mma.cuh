@@ -529,11 +529,26 @@ struct AttTcCfg {
   static constexpr int TM_COLS = 256;                       // S: 64 columns, O: HD columns
 };
 
+// Which keys a query sees besides j <= i.  window > 0: only i - j < window, plus the first `keep_first` keys of the
+// sequence (kept at their true positions); window <= 0: every earlier key (plain causal attention).
+struct AttMask {
+  int window, keep_first;
+};
+// Where the query rows come from and what the epilogue does besides the normalisation.  q row of (token t, head h):
+// q + t * ldq + h * HD (+ qbias[h * HD + .] added in fp32 before the bf16 rounding when qbias != nullptr);
+// gate != nullptr: the output is multiplied by sigmoid(gate[t * ld_gate + h * HD + .]).
+struct AttIo {
+  long long ldq;
+  const float* qbias;
+  const bf16* gate;
+  long long ld_gate;
+};
+
 template <int HD, int G>
 __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const bf16* __restrict__ q,
     BatchMeta m, const int* __restrict__ tile_start, const int* __restrict__ tile_len, bf16* __restrict__ out, int H,
-    int KV, float scale_log2) {
+    int KV, float scale_log2, AttMask mk, AttIo io) {
   using Cfg = AttTcCfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -569,7 +584,20 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
   const int pos0 = m.tok_pos[t0];
   const int slot = m.seq_slot[m.tok_seq[t0]];
   const int* pt = m.page_table + (long long)slot * m.max_pages;
-  const int n_kt = (pos0 + nt - 1) / XB_ATT_TILE + 1;
+  // Key tiles this block visits, in order: with a window, the tiles that hold kept first keys and lie before the window
+  // of the block's first row (nkf of them), then `skip` tiles nobody sees are jumped over; visit i reads tile
+  // i (i < nkf) or i + skip.  Without a window: every tile up to the last row's position.
+  const int last_pos = pos0 + nt - 1;
+  int nkf = 0, skip = 0;
+  if (mk.window > 0) {
+    const int lo_min = pos0 - mk.window + 1 > 0 ? pos0 - mk.window + 1 : 0;
+    const int w0 = lo_min / XB_ATT_TILE;
+    const int kf_tiles = (mk.keep_first + XB_ATT_TILE - 1) / XB_ATT_TILE;
+    nkf = kf_tiles < w0 ? kf_tiles : w0;
+    skip = w0 - nkf;
+  }
+  const int n_kt = last_pos / XB_ATT_TILE + 1 - skip;
+  auto tile_of = [&](int i) { return i < nkf ? i : i + skip; };
 
   if (warp == 1) {
     if (lane == 0) {
@@ -609,7 +637,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     const int rgs = XB_ATT_TILE / BR;                        // boxes (row groups) per tile
     const int n_rg = n_kt * rgs;
     for (int i = lane; i < n_rg && i < XB_ATT_PG_CACHE; i += 32) {
-      const int pi = (i * BR) / P;
+      const int pi = (tile_of(i / rgs) * XB_ATT_TILE + (i % rgs) * BR) / P;
       s_pages[i] = pt[pi < m.max_pages ? pi : m.max_pages - 1];
     }
     __syncwarp();
@@ -620,7 +648,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
         mbar_expect_tx(bar, Cfg::TILE_BYTES);
         for (int rg = 0; rg < rgs; ++rg) {
           const int i = kt * rgs + rg;
-          const int key = kt * XB_ATT_TILE + rg * BR;
+          const int key = tile_of(kt) * XB_ATT_TILE + rg * BR;
           int page;
           if (i < XB_ATT_PG_CACHE) page = s_pages[i];
           else { const int pi = key / P; page = pt[pi < m.max_pages ? pi : m.max_pages - 1]; }
@@ -703,11 +731,20 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     // ---- stage Q into swizzled smem (K-major A operand), zero rows beyond the tile
     {
-      const bf16* qrow = q + ((long long)(t0 + (valid ? tq : 0)) * H + (kvh * G + gq)) * HD;
+      const bf16* qrow = q + (long long)(t0 + (valid ? tq : 0)) * io.ldq + (long long)(kvh * G + gq) * HD;
+      const float* qb = io.qbias != nullptr ? io.qbias + (long long)(kvh * G + gq) * HD : nullptr;
 #pragma unroll
       for (int c = 0; c < HD / 8; ++c) {
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (valid) v = *reinterpret_cast<const uint4*>(qrow + c * 8);
+        if (valid) {
+          v = *reinterpret_cast<const uint4*>(qrow + c * 8);
+          if (qb != nullptr) {
+            const float4 b0 = *reinterpret_cast<const float4*>(qb + c * 8), b1 = *reinterpret_cast<const float4*>(qb + c * 8 + 4);
+            const float2 x0 = bf2_to_f2(v.x), x1 = bf2_to_f2(v.y), x2 = bf2_to_f2(v.z), x3 = bf2_to_f2(v.w);
+            v.x = f2_to_bf2(x0.x + b0.x, x0.y + b0.y); v.y = f2_to_bf2(x1.x + b0.z, x1.y + b0.w);
+            v.z = f2_to_bf2(x2.x + b1.x, x2.y + b1.y); v.w = f2_to_bf2(x3.x + b1.z, x3.y + b1.w);
+          }
+        }
         *reinterpret_cast<uint4*>(sQ + (c >> 3) * (128 * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
       }
       fence_proxy_async();
@@ -719,20 +756,24 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     for (int kt = 0; kt < n_kt; ++kt) {
       mbar_wait(&s_full[kt & 1], (kt >> 1) & 1);
       tc_fence_after();
-      const int key0 = kt * XB_ATT_TILE;
+      const int key0 = tile_of(kt) * XB_ATT_TILE;
       const uint32_t tm_Sk = tm_S + (uint32_t)((kt & 1) * XB_ATT_TILE);
       // ---- the 64 scores of this row: ONE TMEM read, kept in registers for both steps below
       uint32_t v[XB_ATT_TILE];
 #pragma unroll
       for (int c = 0; c < XB_ATT_TILE; c += 16) tmem_ld16(tm_Sk + lane_base + c, v + c);
       tmem_ld_wait();
-      // only tiles that reach past the first row's position need per-element causal masks
-      const bool masked = key0 + XB_ATT_TILE - 1 > pos0;
+      // only tiles that reach past the first row's position, or (with a window) back beyond the last row's window,
+      // need per-element masks.  The row sees key k when k <= lim and (k >= lo_row or k < kf).
+      const bool masked = key0 + XB_ATT_TILE - 1 > pos0 || (mk.window > 0 && last_pos - key0 >= mk.window);
+      const int lo_row = (mk.window > 0 && lim - mk.window + 1 > 0) ? lim - mk.window + 1 : 0;
+      const int kf = mk.window > 0 ? mk.keep_first : 0;
+      auto vis = [&](int k) { return k <= lim && (k >= lo_row || k < kf); };
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains (ILP)
       if (masked) {
 #pragma unroll
         for (int j = 0; j < XB_ATT_TILE; ++j)
-          if (key0 + j <= lim) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
+          if (vis(key0 + j)) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
       } else {
 #pragma unroll
         for (int j = 0; j < XB_ATT_TILE; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
@@ -786,7 +827,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
         if (masked) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            if (key0 + c + j > lim) p[j] = 0.f;
+            if (!vis(key0 + c + j)) p[j] = 0.f;
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) ps[j & 3] += p[j];
@@ -816,6 +857,7 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
     tc_fence_after();
     const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
     bf16* dst = out + ((long long)(t0 + (valid ? tq : 0)) * H + (kvh * G + gq)) * HD;
+    const bf16* gate = io.gate != nullptr ? io.gate + (long long)(t0 + (valid ? tq : 0)) * io.ld_gate + (long long)(kvh * G + gq) * HD : nullptr;
 #pragma unroll 1
     for (int c = 0; c < HD; c += 16) {
       uint32_t v[16];
@@ -825,6 +867,16 @@ __global__ void __launch_bounds__(192, 2) xb_attn_prefill_tc_kernel(
         float x[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) x[j] = __uint_as_float(v[j]) * inv;
+        if (gate != nullptr) {
+          const uint4 g0 = *reinterpret_cast<const uint4*>(gate + c), g1 = *reinterpret_cast<const uint4*>(gate + c + 8);
+          const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 gv = bf2_to_f2(gw[j]);
+            x[2 * j] *= 1.0f / (1.0f + expf(-gv.x));
+            x[2 * j + 1] *= 1.0f / (1.0f + expf(-gv.y));
+          }
+        }
         uint4 w0, w1;
         w0.x = f2_to_bf2(x[0], x[1]);   w0.y = f2_to_bf2(x[2], x[3]);   w0.z = f2_to_bf2(x[4], x[5]);   w0.w = f2_to_bf2(x[6], x[7]);
         w1.x = f2_to_bf2(x[8], x[9]);   w1.y = f2_to_bf2(x[10], x[11]); w1.z = f2_to_bf2(x[12], x[13]); w1.w = f2_to_bf2(x[14], x[15]);

@@ -849,7 +849,8 @@ static int launch_attn_g(xb_engine* e, const LayerW& w, const BatchMeta& m, int 
     using Cfg = AttTcCfg<HD>;
     XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, G>), Cfg::SMEM_BYTES);
     XB_TRY(launch_k(e, xb_attn_prefill_tc_kernel<HD, G>, dim3(n_tiles, d.n_kv_heads), dim3(192), Cfg::SMEM_BYTES, st, 1, w.tmK,
-                    w.tmV, e->q, m, m.tile_start, m.tile_len, e->attn, d.n_heads, d.n_kv_heads, scale_log2));
+                    w.tmV, e->q, m, m.tile_start, m.tile_len, e->attn, d.n_heads, d.n_kv_heads, scale_log2, AttMask{0, 0},
+                    AttIo{(long long)d.n_heads * HD, nullptr, nullptr, 0}));
   }
   return 0;
 }
@@ -955,7 +956,7 @@ static void fill_batch_meta(const xb_engine* e, BatchMeta& m) {
 
 static int run_body(xb_engine* e, int T, int n_seqs, int n_splits, int n_tiles, void* const* taps, cudaStream_t st,
                     int ho_in = 0, int ho_out = 0, int with_head = 1) {
-  if (e->hy != nullptr) return hy_run_body(e, T, n_seqs, taps, st, with_head);
+  if (e->hy != nullptr) return hy_run_body(e, T, n_seqs, n_tiles, taps, st, with_head);
   const xb_model_desc& d = e->d;
   const bool first = shard_is_first(d), last = shard_is_last(d);
   BatchMeta m;
@@ -1308,7 +1309,7 @@ extern "C" int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybr
   e->device = device;
   e->num_sms = prop.multiProcessorCount;
   e->nl = 0;
-  e->tile_tokens = 128;
+  e->tile_tokens = hy_tile_tokens(h, layers);
   int rc = alloc_batch_meta(e);
   if (rc == 0) rc = dmalloc((void**)&e->in_tokens, (size_t)h.max_batch_tokens * 4);
   if (rc == 0) rc = hy_create(e, h, layers);

@@ -27,6 +27,10 @@ struct HyLayer {
   // tile-major copies for the tcgen05 Linear (bf16 serving; made once all weights are in, see hy_finalize)
   bf16 *t_in = nullptr, *t_o = nullptr, *t_o2 = nullptr, *t_up = nullptr, *t_down = nullptr, *t_sgate = nullptr, *t_sproj = nullptr;
   void *k_pool = nullptr, *v_pool = nullptr;
+  // bf16 serving, key and value heads of one size (64 or 128) and at most 8 query heads per key head: prompts run through the
+  // engine's tcgen05 attention (window and kept first keys as its mask), reading the pools through these tensor maps
+  bool tc_attn = false;
+  CUtensorMap tmK, tmV;
   size_t st_rec = 0, st_conv = 0, st_canon1 = 0, st_canon2 = 0;   // float offsets inside a slot's state
 };
 
@@ -38,7 +42,7 @@ struct HyModel {
   float* state = nullptr;
   size_t state_floats = 0;   // per slot
   float *x = nullptr, *hn = nullptr, *P = nullptr, *c = nullptr, *o = nullptr, *m1 = nullptr, *m2 = nullptr, *beta = nullptr,
-        *decay = nullptr, *head_raw = nullptr;
+        *decay = nullptr, *qk = nullptr, *head_raw = nullptr;
   void *a1 = nullptr, *a2 = nullptr, *head_in = nullptr;
   int* d_rows = nullptr;
   size_t maxN = 0, maxK = 0, maxC = 0, maxO = 0, maxH = 1;
@@ -113,7 +117,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     }
     if (c.mixer == XB_MIX_DELTA) {
       const long long H = c.d_heads, G = c.d_kv_heads, dk = c.d_dim, dv = c.d_vdim, tp = c.d_taps;
-      XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 32 * HY_MAX_KREG && dv > 0, "layer %d: bad delta-rule sizes (key dim <= %d)", i, 32 * HY_MAX_KREG);
+      XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= HY_MAX_KDIM && dv > 0, "layer %d: bad delta-rule sizes (key dim <= %d)", i, HY_MAX_KDIM);
       XB_CHECK(tp >= 1 && tp <= HY_MAX_TAPS, "layer %d: short filter of %lld taps (1..%d)", i, tp, HY_MAX_TAPS);
       l.off_q = 0; l.off_k = (int)(G * dk); l.off_v = (int)(2 * G * dk);
       l.c_conv = (int)(2 * G * dk + H * dv);
@@ -151,7 +155,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       const long long Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
       XB_CHECK(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 256, "layer %d: bad attention sizes (value dim <= 256)", i);
       XB_CHECK(c.a_window >= 1 && c.a_keep_first >= 0, "layer %d: bad window %d / kept first tokens %d", i, c.a_window, c.a_keep_first);
-      XB_CHECK(Hr > 0 && rk > 0 && rk <= 32 * HY_MAX_KREG && rv > 0, "layer %d: bad HGRN2 sizes (key dim <= %d)", i, 32 * HY_MAX_KREG);
+      XB_CHECK(Hr > 0 && rk > 0 && rk <= HY_MAX_KDIM && rv > 0, "layer %d: bad HGRN2 sizes (key dim <= %d)", i, HY_MAX_KDIM);
       l.off_q = 0; l.off_k = (int)(H * dk); l.off_v = l.off_k + (int)(G * dk); l.off_g = l.off_v + (int)(G * dv);
       l.off_rq = l.off_g + (int)(H * dv); l.off_rf = l.off_rq + (int)(Hr * rk); l.off_rv = l.off_rf + (int)(Hr * rk);
       l.n_in = l.off_rv + (int)(Hr * rv);
@@ -173,6 +177,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       hy_name_vec(hy, p + "mix.right.lower", l.lower, Hr * rk);
       hy_name_vec(hy, p + "mix.right.norm", l.head_norm, rv);
       hy_name_rows(hy, p + "mix.right.o", l.w_o2, 0, D, l.n_o2);
+      l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8 && c.a_scale > 0.f;
       l.st_rec = st; st += (size_t)(Hr * rv * rk);
       const size_t cc = (size_t)(2 * Hr * rk + Hr * rv);
       if (cc > hy->maxC) hy->maxC = cc;
@@ -231,6 +236,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   XB_TRY(hy_alloc(hy, (void**)&hy->m2, hy->cap_m));
   XB_TRY(hy_alloc_t(hy, &hy->beta, Tm * hy->maxH));
   XB_TRY(hy_alloc_t(hy, &hy->decay, Tm * hy->maxH));
+  XB_TRY(hy_alloc_t(hy, &hy->qk, Tm * hy->maxH));
   XB_TRY(hy_alloc(hy, &hy->a1, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->a2, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->head_in, R * D * as));
@@ -364,6 +370,12 @@ static int hy_reserve(xb_engine* e) {
     XB_TRY(dmalloc(&l.v_pool, vb));
     XB_CUDA(cudaMemset(l.k_pool, 0, kb));
     XB_CUDA(cudaMemset(l.v_pool, 0, vb));
+    if (l.tc_attn) {
+      const long long pool_rows = (long long)e->n_pages * l.d.a_kv_heads * e->page_tokens;
+      const int box_rows = e->page_tokens < 64 ? e->page_tokens : 64;
+      XB_TRY(xb_make_tmap(&l.tmK, l.k_pool, pool_rows, l.d.a_dim, l.d.a_dim, box_rows));
+      XB_TRY(xb_make_tmap(&l.tmV, l.v_pool, pool_rows, l.d.a_vdim, l.d.a_vdim, box_rows));
+    }
   }
   cudaFree(hy->state);
   hy->state = nullptr;
@@ -371,6 +383,19 @@ static int hy_reserve(xb_engine* e) {
   XB_TRY(dmalloc((void**)&hy->state, sb));
   XB_CUDA(cudaMemset(hy->state, 0, sb));
   return 0;
+}
+
+// Query tiles of the tcgen05 attention hold 128 rows = tokens x (query heads per key head); one tile table serves every
+// attention layer, so it is cut for the largest group among them.
+static int hy_tile_tokens(const xb_hybrid_desc& d, const xb_hybrid_layer* layers) {
+  int tt = 128;
+  for (int i = 0; i < d.n_layers; ++i) {
+    const xb_hybrid_layer& c = layers[i];
+    if (c.mixer != XB_MIX_PARALLEL || c.a_kv_heads <= 0 || c.a_heads % c.a_kv_heads != 0) continue;
+    const int group = c.a_heads / c.a_kv_heads;
+    if (group >= 1 && group <= 8 && 128 / group < tt) tt = 128 / group;
+  }
+  return tt;
 }
 
 // ----------------------------------------------------------------------------- forward
@@ -439,6 +464,51 @@ static int hy_linear(xb_engine* e, const void* x, long long ldx, const bf16* w, 
   return 0;
 }
 
+// one recurrence launch: the instance with the fewest 16-row chunks per lane quad that cover the key dim
+template <bool DELTA>
+static int hy_recur(xb_engine* e, const RecurIn& in, float* state, long long ss, float* o, long long ldo, const BatchMeta& m, int n_seqs,
+                    int H, int dk, int dv, cudaStream_t st) {
+  const dim3 grid(n_seqs, H, (dv + HY_RC_COLS - 1) / HY_RC_COLS);
+#define HY_RECUR_CASE(NCH)                                                                                         \
+  if (dk <= 16 * NCH) {                                                                                            \
+    const size_t smem = (size_t)2 * HY_TS * (2 * 16 * NCH + HY_RC_COLS + 4) * sizeof(float);                       \
+    if (smem > 48 * 1024) XB_SMEM_ATTR_ONCE((hy_recur_kernel<NCH, DELTA>), smem);                                  \
+    return hy_launch(e, hy_recur_kernel<NCH, DELTA>, grid, dim3(128), smem, st, in, state, ss, o, ldo, m, H, dk, dv); \
+  }
+  HY_RECUR_CASE(1)
+  HY_RECUR_CASE(2)
+  HY_RECUR_CASE(4)
+  HY_RECUR_CASE(8)
+  HY_RECUR_CASE(16)
+#undef HY_RECUR_CASE
+  return xb_fail(1, "recurrent key dim %d exceeds %d", dk, HY_MAX_KDIM);
+}
+
+template <int HD, int GRP>
+static int hy_attn_tc_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, int n_tiles, const LinOut& P, bf16* out, cudaStream_t st) {
+  using Cfg = AttTcCfg<HD>;
+  const xb_hybrid_layer& c = l.d;
+  XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, GRP>), Cfg::SMEM_BYTES);
+  const AttMask mk{c.a_window, c.a_keep_first};
+  const AttIo io{P.ld, P.bias != nullptr ? P.bias + l.off_q : nullptr, P.h + l.off_g, P.ld};
+  return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP>, dim3(n_tiles, c.a_kv_heads), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV,
+                   P.h + l.off_q, m, m.tile_start, m.tile_len, out, c.a_heads, c.a_kv_heads, c.a_scale * 1.4426950408889634f, mk, io);
+}
+template <int HD>
+static int hy_attn_tc(xb_engine* e, const HyLayer& l, const BatchMeta& m, int n_tiles, const LinOut& P, bf16* out, cudaStream_t st) {
+  switch (l.d.a_heads / l.d.a_kv_heads) {
+    case 1: return hy_attn_tc_g<HD, 1>(e, l, m, n_tiles, P, out, st);
+    case 2: return hy_attn_tc_g<HD, 2>(e, l, m, n_tiles, P, out, st);
+    case 3: return hy_attn_tc_g<HD, 3>(e, l, m, n_tiles, P, out, st);
+    case 4: return hy_attn_tc_g<HD, 4>(e, l, m, n_tiles, P, out, st);
+    case 5: return hy_attn_tc_g<HD, 5>(e, l, m, n_tiles, P, out, st);
+    case 6: return hy_attn_tc_g<HD, 6>(e, l, m, n_tiles, P, out, st);
+    case 7: return hy_attn_tc_g<HD, 7>(e, l, m, n_tiles, P, out, st);
+    case 8: return hy_attn_tc_g<HD, 8>(e, l, m, n_tiles, P, out, st);
+  }
+  return xb_fail(1, "no tcgen05 attention for %d query heads per key head", l.d.a_heads / l.d.a_kv_heads);
+}
+
 template <typename AT>
 static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float s2, const float* bw, float bw_one, const float* nw,
                      void* xa, cudaStream_t st) {
@@ -467,7 +537,7 @@ static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, const float* w, si
 }
 
 template <typename AT>
-static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cudaStream_t st, int with_head) {
+static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
   HyModel* hy = e->hy;
   const xb_hybrid_desc& d = hy->d;
   typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
@@ -501,9 +571,13 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
       if (tp > 1)
         XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (l.c_conv + 255) / 256), dim3(256), 0, st, P, 0, l.c_conv, tp, tail, SS, m));
       XB_TRY(hy_launch(e, hy_delta_prep_kernel, dim3(T), dim3(256), 0, st, hy->c, (long long)l.c_conv, P, l.off_b, l.off_a,
-                       (const float*)l.A_log, (const float*)l.dt_bias, hy->beta, hy->decay, H, G, dk));
-      XB_TRY(hy_launch(e, hy_delta_rule_kernel, dim3(n_seqs, H, (dv + 7) / 8), dim3(256), (size_t)HY_TS * (2 * dk + 10) * sizeof(float), st, (const float*)hy->c, (long long)l.c_conv,
-                       (const float*)hy->beta, (const float*)hy->decay, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, H, G, dk, dv));
+                       (const float*)l.A_log, (const float*)l.dt_bias, hy->beta, hy->decay, hy->qk, H, G, dk));
+      {
+        RecurIn in;
+        in.c = hy->c; in.ldc = l.c_conv; in.qoff = 0; in.koff = (long long)G * dk; in.voff = 2LL * G * dk; in.q_heads = G;
+        in.beta = hy->beta; in.decay = hy->decay; in.qk = hy->qk;
+        XB_TRY(hy_recur<true>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, n_seqs, H, dk, dv, st));
+      }
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (H + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
                        (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
@@ -511,7 +585,12 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
       const int Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
       XB_TRY(hy_launch(e, hy_kv_append_kernel<KT>, dim3(T, (G * (dk + dv) + 255) / 256), dim3(256), 0, st, P, l.off_k, l.off_v, (KT*)l.k_pool, (KT*)l.v_pool, m, G, dk, dv));
-      {
+      // a prompt's portion whose projection came back as a bf16 matrix: the tcgen05 kernel (16-byte loads of q and gate rows)
+      const bool tc = std::is_same<AT, bf16>::value && l.tc_attn && n_tiles > 0 && P.h != nullptr && P.ld % 8 == 0 && l.off_g % 8 == 0;
+      if (tc) {
+        if (dk == 128) XB_TRY(hy_attn_tc<128>(e, l, m, n_tiles, P, reinterpret_cast<bf16*>(hy->a1), st));
+        else XB_TRY(hy_attn_tc<64>(e, l, m, n_tiles, P, reinterpret_cast<bf16*>(hy->a1), st));
+      } else {
         // warps per (token, head): one per 64 visible keys, at most 8
         int aw = (c.a_window + c.a_keep_first + 63) / 64;
         aw = aw < 1 ? 1 : (aw > 8 ? 8 : aw);
@@ -523,8 +602,12 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
       const long long ldc = 2LL * Hr * rk + (long long)Hr * rv;
       XB_TRY(hy_launch(e, hy_hgrn_prep_kernel, dim3(T, (2 * Hr * rk + Hr * rv + 255) / 256), dim3(256), 0, st, P, l.off_rq, l.off_rf, l.off_rv, (const float*)l.lower, hy->c,
                        ldc, Hr * rk, Hr * rv));
-      XB_TRY(hy_launch(e, hy_hgrn_kernel, dim3(n_seqs, Hr, (rv + 7) / 8), dim3(256), (size_t)HY_TS * (2 * rk + 8) * sizeof(float), st, (const float*)hy->c, ldc,
-                       hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, Hr, rk, rv));
+      {
+        RecurIn in;
+        in.c = hy->c; in.ldc = ldc; in.qoff = 0; in.koff = (long long)Hr * rk; in.voff = 2LL * Hr * rk; in.q_heads = Hr;
+        in.beta = in.decay = in.qk = nullptr;
+        XB_TRY(hy_recur<false>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, n_seqs, Hr, rk, rv, st));
+      }
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (Hr + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o2,
                        (const float*)l.head_norm, P, -1, d.norm_eps, 1.0f, a2, (long long)l.n_o2, Hr, rv));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
@@ -571,7 +654,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, void* const* taps, cud
   return 0;
 }
 
-static int hy_run_body(xb_engine* e, int T, int n_seqs, void* const* taps, cudaStream_t st, int with_head) {
-  if (e->hy->d.compute_fp32) return hy_run_body_t<float>(e, T, n_seqs, taps, st, with_head);
-  return hy_run_body_t<bf16>(e, T, n_seqs, taps, st, with_head);
+static int hy_run_body(xb_engine* e, int T, int n_seqs, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
+  if (e->hy->d.compute_fp32) return hy_run_body_t<float>(e, T, n_seqs, n_tiles, taps, st, with_head);
+  return hy_run_body_t<bf16>(e, T, n_seqs, n_tiles, taps, st, with_head);
 }

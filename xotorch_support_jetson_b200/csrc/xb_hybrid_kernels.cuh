@@ -15,7 +15,7 @@
 #include <math.h>
 
 #define HY_MAX_TAPS 16   // causal filters keep taps - 1 inputs per sequence
-#define HY_MAX_KREG 8    // recurrent state: a warp owns one value column, lane l holds rows l, l + 32, ... (key dim <= 256)
+#define HY_MAX_KDIM 256  // recurrent state: four lanes own one value column, up to 64 rows each
 
 struct LinOut {
   const float* f;      // fp32 [planes][T][ld] (planes summed per column, see SplitInfo), or nullptr
@@ -289,22 +289,28 @@ __global__ void __launch_bounds__(256) hy_linear_tiled_kernel(const AT* __restri
 // ----------------------------------------------------------------------------- gated delta rule
 // Inputs per token: q, k (kv_heads x dk) and v (heads x dv) after the short filter + SiLU, in `c` [T, 2*G*dk + H*dv];
 // the fused projection P also carries the read-out gate (H*dv), b (H) and a (H) columns.
-// Prep, one block per token: q and k to unit length per head (q also times dk^-1/2), beta = sigmoid(b),
-// decay = exp(-exp(A_log) * softplus(a + dt_bias)).
+// Prep, one block per token: q and k to unit length per head (q also times dk^-1/2) and their product q . k per
+// q/k head, beta = sigmoid(b), decay = exp(-exp(A_log) * softplus(a + dt_bias)).
 __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ c, long long ldc, LinOut P, int off_b, int off_a,
                                                             const float* __restrict__ A_log, const float* __restrict__ dt_bias,
-                                                            float* __restrict__ beta, float* __restrict__ decay, int H, int G, int dk) {
+                                                            float* __restrict__ beta, float* __restrict__ decay, float* __restrict__ qk,
+                                                            int H, int G, int dk) {
   const long long t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   float* row = c + t * ldc;
-  for (int u = warp; u < 2 * G; u += nw) {   // u < G: q head u; else k head u - G (q block, then k block)
-    float* p = row + (long long)u * dk;
-    float ss = 0.f;
-    for (int i = lane; i < dk; i += 32) ss += p[i] * p[i];
-    ss = warp_sum(ss);
-    float sc = 1.0f / sqrtf(ss + 1e-6f);
-    if (u < G) sc *= 1.0f / sqrtf((float)dk);
-    for (int i = lane; i < dk; i += 32) p[i] *= sc;
+  for (int g = warp; g < G; g += nw) {   // q block, then k block
+    float* pq = row + (long long)g * dk;
+    float* pk = row + (long long)(G + g) * dk;
+    float sq = 0.f, sk = 0.f, d = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+      const float a = pq[i], b = pk[i];
+      sq = fmaf(a, a, sq); sk = fmaf(b, b, sk); d = fmaf(a, b, d);
+    }
+    sq = warp_sum(sq); sk = warp_sum(sk); d = warp_sum(d);
+    const float cq = 1.0f / sqrtf(sq + 1e-6f) * (1.0f / sqrtf((float)dk));
+    const float ck = 1.0f / sqrtf(sk + 1e-6f);
+    for (int i = lane; i < dk; i += 32) { pq[i] *= cq; pk[i] *= ck; }
+    if (lane == 0) qk[t * G + g] = d * cq * ck;
   }
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     beta[t * H + h] = hy_sigmoid(lin_at(P, t, off_b + h));
@@ -312,82 +318,172 @@ __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ 
   }
 }
 
-// Recurrence.  Per head the state is S [dk, dv]; every value column evolves alone:
-//   S_j <- g S_j;  u_j = beta (v_j - k . S_j);  S_j <- S_j + k u_j;  o_j = q . S_j
-// so a warp owns one column (lane l holds rows l, l+32, ...), and with a = k . S_j, b = q . S_j, qk = q . k taken on
-// the OLD column in one reduction: u_j = beta (v_j - g a), o_j = g b + qk u_j.
-// The warps of a block share (sequence, head): the inputs of HY_TS steps (q, k, the block's v columns, beta, decay) are
-// staged in shared memory with coalesced loads, then every warp walks the steps from there.
-// grid (n_seqs, H, ceil(dv / warps)); state [slot][H][dv][dk] fp32; dynamic smem HY_TS * (2 dk + warps + 2) floats.
+// Recurrences.  Per head the state is S [dk, dv] and every value column j evolves alone:
+//   delta rule: S_j <- g S_j;  u_j = beta (v_j - k . S_j);  S_j <- S_j + k u_j;  o_j = q . S_j
+//               with a = k . S_j and b = q . S_j taken on the OLD column: u_j = beta (v_j - g a), o_j = g b + (q . k) u_j
+//   HGRN2:      S_j <- f * S_j + (1 - f) v_j;  o_j = q . S_j      (f per row, in the k slot of the inputs)
+// Four lanes own one column: lane `sub` holds the rows of the 16-byte chunks sub, sub + 4, ... (NCH chunks, rows beyond
+// dk are zero), so a dot product over the rows ends in two shuffles and a warp carries 8 columns.  The 4 warps of a
+// block share (sequence, head) and 32 columns; the inputs of HY_TS steps (q, k or f, the block's v columns, and for the
+// delta rule beta, decay and q . k) arrive in shared memory by cp.async, one chunk of steps ahead of the arithmetic.
+// grid (n_seqs, H, ceil(dv / 32)), 128 threads; state [slot][H][dv][dk] fp32;
+// dynamic shared memory 2 * HY_TS * (2 * 16 * NCH + 36) floats.
 #define HY_TS 16
-__global__ void __launch_bounds__(256) hy_delta_rule_kernel(const float* __restrict__ c, long long ldc, const float* __restrict__ beta,
-                                                            const float* __restrict__ decay, float* __restrict__ state,
-                                                            long long state_stride, float* __restrict__ o, long long ldo, BatchMeta m,
-                                                            int H, int G, int dk, int dv) {
-  extern __shared__ float stg[];
+#define HY_RC_COLS 32
+struct RecurIn {
+  const float* c;        // [T, ldc] prepared inputs
+  long long ldc;
+  long long qoff, koff, voff;   // columns of head 0's q, k (or f) and v; heads follow at q_stride / k_stride / dv
+  int q_heads;           // delta rule: heads share q / k in groups (q head = h / (H / q_heads)); HGRN2: = H
+  const float *beta, *decay, *qk;   // delta rule: [T, H], [T, H], [T, q_heads]
+};
+__device__ __forceinline__ void hy_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void hy_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void hy_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void hy_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int NCH, bool DELTA>
+__global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __restrict__ state, long long state_stride, float* __restrict__ o,
+                                                       long long ldo, BatchMeta m, int H, int dk, int dv) {
+  extern __shared__ __align__(16) float stg[];
+  constexpr int DKP = 16 * NCH;                 // padded key dim
+  constexpr int STRIDE = 2 * DKP + HY_RC_COLS + 4;
   const int s = blockIdx.x, h = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int j0 = blockIdx.z * nw, j = j0 + warp;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 3;
+  const int j0 = blockIdx.z * HY_RC_COLS, jl = warp * 8 + (lane >> 2), j = j0 + jl;
   const bool live = j < dv;
+  const int ncv = dv - j0 < HY_RC_COLS ? dv - j0 : HY_RC_COLS;
   const SeqSpan sp = seq_span(m, s);
-  const int g = h / (H / G);
+  const int g = h / (H / in.q_heads);
+  const float* cq = in.c + in.qoff + (long long)g * dk;
+  const float* ck = in.c + in.koff + (long long)g * dk;
+  const float* cv = in.c + in.voff + (long long)h * dv + j0;
+  // 16-byte copies when every row piece starts on a 16-byte boundary
+  const bool al = ((in.ldc | in.qoff | in.koff | in.voff | dk | dv) & 3) == 0 && (reinterpret_cast<uintptr_t>(in.c) & 15) == 0;
+  for (int i = threadIdx.x; i < 2 * HY_TS * STRIDE; i += blockDim.x) stg[i] = 0.f;   // padding rows / columns stay zero
   float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + (live ? j : 0)) * dk;
-  float S[HY_MAX_KREG];
+  float S[4 * NCH];
+  {
+    const bool have = live && sp.pos0 > 0;
+    const bool st_al = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(st) & 15) == 0;
 #pragma unroll
-  for (int i = 0; i < HY_MAX_KREG; ++i) {
-    const int r = lane + 32 * i;
-    S[i] = (live && sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int r = (ch * 4 + sub) * 4;
+      if (have && st_al && r + 3 < dk) {
+        const float4 v = *reinterpret_cast<const float4*>(st + r);
+        S[4 * ch] = v.x; S[4 * ch + 1] = v.y; S[4 * ch + 2] = v.z; S[4 * ch + 3] = v.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[4 * ch + e] = (have && r + e < dk) ? st[r + e] : 0.f;
+      }
+    }
   }
-  const long long qoff = (long long)g * dk, koff = (long long)(G + g) * dk, voff = (long long)2 * G * dk + (long long)h * dv + j0;
-  const int stride = 2 * dk + nw + 2;
-  for (int t0 = 0; t0 < sp.len; t0 += HY_TS) {
+  __syncthreads();
+  auto stage = [&](int t0, float* buf) {
     const int nt = sp.len - t0 < HY_TS ? sp.len - t0 : HY_TS;
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * stride; idx += blockDim.x) {
-      const int ts = idx / stride, cc = idx - ts * stride;
-      const long long row = sp.start + t0 + ts;
-      const float* cr = c + row * ldc;
-      float v;
-      if (cc < dk) v = cr[qoff + cc];
-      else if (cc < 2 * dk) v = cr[koff + cc - dk];
-      else if (cc < 2 * dk + nw) v = (j0 + cc - 2 * dk < dv) ? cr[voff + cc - 2 * dk] : 0.f;
-      else if (cc == 2 * dk + nw) v = beta[row * H + h];
-      else v = decay[row * H + h];
-      stg[idx] = v;
+    if (al) {
+      const int dq = dk >> 2, per = 2 * dq + (ncv >> 2);
+      for (int idx = threadIdx.x; idx < nt * per; idx += blockDim.x) {
+        const int ts = idx / per, u = idx - ts * per;
+        const long long row = (long long)(sp.start + t0 + ts) * in.ldc;
+        float* d = buf + ts * STRIDE;
+        if (u < dq) hy_cp16(d + 4 * u, cq + row + 4 * u);
+        else if (u < 2 * dq) hy_cp16(d + DKP + 4 * (u - dq), ck + row + 4 * (u - dq));
+        else hy_cp16(d + 2 * DKP + 4 * (u - 2 * dq), cv + row + 4 * (u - 2 * dq));
+      }
+    } else {
+      const int per = 2 * dk + ncv;
+      for (int idx = threadIdx.x; idx < nt * per; idx += blockDim.x) {
+        const int ts = idx / per, u = idx - ts * per;
+        const long long row = (long long)(sp.start + t0 + ts) * in.ldc;
+        float* d = buf + ts * STRIDE;
+        if (u < dk) hy_cp4(d + u, cq + row + u);
+        else if (u < 2 * dk) hy_cp4(d + DKP + (u - dk), ck + row + (u - dk));
+        else hy_cp4(d + 2 * DKP + (u - 2 * dk), cv + row + (u - 2 * dk));
+      }
     }
+    if (DELTA) {
+      for (int idx = threadIdx.x; idx < nt * 3; idx += blockDim.x) {
+        const int ts = idx / 3, u = idx - ts * 3;
+        const long long row = sp.start + t0 + ts;
+        const float* src = u == 0 ? in.beta + row * H + h : (u == 1 ? in.decay + row * H + h : in.qk + row * in.q_heads + g);
+        hy_cp4(buf + ts * STRIDE + 2 * DKP + HY_RC_COLS + u, src);
+      }
+    }
+    hy_cp_commit();
+  };
+  stage(0, stg);
+  int cur = 0;
+  for (int t0 = 0; t0 < sp.len; t0 += HY_TS, cur ^= 1) {
+    const int nt = sp.len - t0 < HY_TS ? sp.len - t0 : HY_TS;
+    const bool more = t0 + HY_TS < sp.len;
+    if (more) { stage(t0 + HY_TS, stg + (cur ^ 1) * HY_TS * STRIDE); hy_cp_wait<1>(); }
+    else hy_cp_wait<0>();
     __syncthreads();
-    if (!live) continue;
+    const float* buf = stg + cur * HY_TS * STRIDE;
     for (int ts = 0; ts < nt; ++ts) {
-      const float* sr = stg + ts * stride;
-      float kv[HY_MAX_KREG];
-      float a = 0.f, b = 0.f, qk = 0.f;
+      const float* sr = buf + ts * STRIDE;
+      const float v = sr[2 * DKP + jl];
+      if (DELTA) {
+        float kv[4 * NCH];
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < HY_MAX_KREG; ++i) {
-        const int r = lane + 32 * i;
-        const float qv = r < dk ? sr[r] : 0.f;
-        kv[i] = r < dk ? sr[dk + r] : 0.f;
-        a = fmaf(kv[i], S[i], a);
-        b = fmaf(qv, S[i], b);
-        qk = fmaf(qv, kv[i], qk);
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int r = (ch * 4 + sub) * 4;
+          const float4 q4 = *reinterpret_cast<const float4*>(sr + r);
+          const float4 k4 = *reinterpret_cast<const float4*>(sr + DKP + r);
+          kv[4 * ch] = k4.x; kv[4 * ch + 1] = k4.y; kv[4 * ch + 2] = k4.z; kv[4 * ch + 3] = k4.w;
+          a0 = fmaf(k4.x, S[4 * ch], a0); a1 = fmaf(k4.y, S[4 * ch + 1], a1);
+          a0 = fmaf(k4.z, S[4 * ch + 2], a0); a1 = fmaf(k4.w, S[4 * ch + 3], a1);
+          b0 = fmaf(q4.x, S[4 * ch], b0); b1 = fmaf(q4.y, S[4 * ch + 1], b1);
+          b0 = fmaf(q4.z, S[4 * ch + 2], b0); b1 = fmaf(q4.w, S[4 * ch + 3], b1);
+        }
+        float a = a0 + a1, b = b0 + b1;
+        a += __shfl_xor_sync(0xffffffffu, a, 1); b += __shfl_xor_sync(0xffffffffu, b, 1);
+        a += __shfl_xor_sync(0xffffffffu, a, 2); b += __shfl_xor_sync(0xffffffffu, b, 2);
+        const float be = sr[2 * DKP + HY_RC_COLS], gd = sr[2 * DKP + HY_RC_COLS + 1], qk = sr[2 * DKP + HY_RC_COLS + 2];
+        const float u = be * (v - gd * a);
+#pragma unroll
+        for (int i = 0; i < 4 * NCH; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
+        if (sub == 0 && live) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = fmaf(qk, u, gd * b);
+      } else {
+        float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int r = (ch * 4 + sub) * 4;
+          const float4 q4 = *reinterpret_cast<const float4*>(sr + r);
+          const float4 f4 = *reinterpret_cast<const float4*>(sr + DKP + r);
+          S[4 * ch] = fmaf(f4.x, S[4 * ch], (1.0f - f4.x) * v);
+          S[4 * ch + 1] = fmaf(f4.y, S[4 * ch + 1], (1.0f - f4.y) * v);
+          S[4 * ch + 2] = fmaf(f4.z, S[4 * ch + 2], (1.0f - f4.z) * v);
+          S[4 * ch + 3] = fmaf(f4.w, S[4 * ch + 3], (1.0f - f4.w) * v);
+          b0 = fmaf(q4.x, S[4 * ch], b0); b1 = fmaf(q4.y, S[4 * ch + 1], b1);
+          b0 = fmaf(q4.z, S[4 * ch + 2], b0); b1 = fmaf(q4.w, S[4 * ch + 3], b1);
+        }
+        float b = b0 + b1;
+        b += __shfl_xor_sync(0xffffffffu, b, 1);
+        b += __shfl_xor_sync(0xffffffffu, b, 2);
+        if (sub == 0 && live) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = b;
       }
-      const float v = sr[2 * dk + warp], be = sr[2 * dk + nw], gd = sr[2 * dk + nw + 1];
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        a += __shfl_xor_sync(0xffffffffu, a, off);
-        b += __shfl_xor_sync(0xffffffffu, b, off);
-        qk += __shfl_xor_sync(0xffffffffu, qk, off);
-      }
-      const float u = be * (v - gd * a);
-#pragma unroll
-      for (int i = 0; i < HY_MAX_KREG; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
-      if (lane == 0) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = fmaf(qk, u, gd * b);
     }
+    __syncthreads();   // the buffer is refilled by the next iteration's copies
   }
   if (live) {
+    const bool st_al = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(st) & 15) == 0;
 #pragma unroll
-    for (int i = 0; i < HY_MAX_KREG; ++i) {
-      const int r = lane + 32 * i;
-      if (r < dk) st[r] = S[i];
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int r = (ch * 4 + sub) * 4;
+      if (st_al && r + 3 < dk) {
+        *reinterpret_cast<float4*>(st + r) = make_float4(S[4 * ch], S[4 * ch + 1], S[4 * ch + 2], S[4 * ch + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (r + e < dk) st[r + e] = S[4 * ch + e];
+      }
     }
   }
 }
@@ -408,67 +504,7 @@ __global__ void hy_hgrn_prep_kernel(LinOut P, int off_q, int off_f, int off_v, c
   c[t * ldc + i] = v;
 }
 
-// Recurrence per head: S <- diag(f) S + (1 - f) v^T, o = S^T q.  Column j: S_j <- f * S_j + (1 - f) v_j, o_j = q . S_j.
-// Same layout as the delta rule: a warp per value column, inputs of HY_TS steps staged in shared memory.
-// dynamic smem HY_TS * (2 dk + warps) floats.
-__global__ void __launch_bounds__(256) hy_hgrn_kernel(const float* __restrict__ c, long long ldc, float* __restrict__ state,
-                                                      long long state_stride, float* __restrict__ o, long long ldo, BatchMeta m, int H,
-                                                      int dk, int dv) {
-  extern __shared__ float stg[];
-  const int s = blockIdx.x, h = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int j0 = blockIdx.z * nw, j = j0 + warp;
-  const bool live = j < dv;
-  const SeqSpan sp = seq_span(m, s);
-  float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + (live ? j : 0)) * dk;
-  float S[HY_MAX_KREG];
-#pragma unroll
-  for (int i = 0; i < HY_MAX_KREG; ++i) {
-    const int r = lane + 32 * i;
-    S[i] = (live && sp.pos0 > 0 && r < dk) ? st[r] : 0.f;
-  }
-  const long long HK = (long long)H * dk;
-  const long long qoff = (long long)h * dk, foff = HK + (long long)h * dk, voff = 2 * HK + (long long)h * dv + j0;
-  const int stride = 2 * dk + nw;
-  for (int t0 = 0; t0 < sp.len; t0 += HY_TS) {
-    const int nt = sp.len - t0 < HY_TS ? sp.len - t0 : HY_TS;
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * stride; idx += blockDim.x) {
-      const int ts = idx / stride, cc = idx - ts * stride;
-      const float* cr = c + (long long)(sp.start + t0 + ts) * ldc;
-      float v;
-      if (cc < dk) v = cr[qoff + cc];
-      else if (cc < 2 * dk) v = cr[foff + cc - dk];
-      else v = (j0 + cc - 2 * dk < dv) ? cr[voff + cc - 2 * dk] : 0.f;
-      stg[idx] = v;
-    }
-    __syncthreads();
-    if (!live) continue;
-    for (int ts = 0; ts < nt; ++ts) {
-      const float* sr = stg + ts * stride;
-      const float v = sr[2 * dk + warp];
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < HY_MAX_KREG; ++i) {
-        const int r = lane + 32 * i;
-        if (r < dk) {
-          const float f = sr[dk + r];
-          S[i] = fmaf(f, S[i], (1.0f - f) * v);
-          acc = fmaf(sr[r], S[i], acc);
-        }
-      }
-      acc = warp_sum(acc);
-      if (lane == 0) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = acc;
-    }
-  }
-  if (live) {
-#pragma unroll
-    for (int i = 0; i < HY_MAX_KREG; ++i) {
-      const int r = lane + 32 * i;
-      if (r < dk) st[r] = S[i];
-    }
-  }
-}
+// The recurrence itself runs in hy_recur_kernel<., false> above: f sits where the delta rule has k.
 
 // ----------------------------------------------------------------------------- per-head RMS norm (+ SiLU gate) of a read-out
 // out[t, h*dv + j] = scale * o / rms_over_dv(o) * w[j] * (gate ? silu(P[t, off_gate + h*dv + j]) : 1)
