@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XB_ABI_VERSION 4
+#define XB_ABI_VERSION 5
 
 typedef struct xb_engine xb_engine;
 
@@ -93,6 +93,7 @@ typedef struct xb_counters {
   uint64_t weight_bytes;      /* bf16 bytes of this shard's matrices read by one decode step */
   uint64_t kv_bytes_per_pos;  /* K+V bytes per cached position over this shard's layers */
   uint64_t kv_pages_total, kv_pages_free;
+  uint64_t tc_attention;      /* launches of the tcgen05 prompt attention kernel */
 } xb_counters;
 
 const char* xb_last_error(void);

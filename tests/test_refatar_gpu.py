@@ -255,6 +255,87 @@ def test_far_key_among_hundreds_in_kept_first(lib):
   assert rel(O.forward(cfg, w, ids2)[390:], ref[390:]) > 0.05     # the far key matters
 
 
+# ----------------------------------------------------------------------------- bf16 serving kernels
+def planted64(window, keep, heads=6, kv=2):
+  """planted() at the head sizes the tensor-core prompt attention takes (key and value heads of 64), bf16 weights."""
+  cfg = config([(pair(heads=heads, kv=kv, dim=64, vdim=64, window=window, keep=keep, rs=0.0, ls=1.0, scale=1.0), 0)], width=128, vocab=50,
+               taps=0, side=0, softcap=0)
+  w = {k: v.float() for k, v in weights(cfg, seed=9).items()}
+  w["embed"][1] *= 0.0
+  w["embed"][1, 0] = 6.0
+  w["l0.mix.left.k"][:, 0] = 0.0
+  w["l0.mix.left.k"][0::64, 0] = 3.0
+  w["l0.mix.left.q.b"][0::64] = 4.0
+  w["l0.mix.left.v"][:, 0] = 2.0
+  return cfg, {k: v.to(torch.bfloat16) for k, v in w.items()}
+
+
+@pytest.mark.parametrize("window,keep,heads,kv", [(100, 5, 6, 2), (64, 0, 4, 4), (70, 66, 8, 1), (1, 0, 2, 1)])
+def test_tensor_core_prompt_attention_edges(lib, window, keep, heads, kv):
+  """Prompts long enough for the bf16 projections to come back as matrices run the tcgen05 attention: 64-key tiles are
+  visited through the kept-first / window map, so the planted key sits at tile borders, at the window's two edges and
+  among the kept first keys, in a whole prompt and in a second portion that starts far from position 0."""
+  cfg, w = planted64(window, keep, heads, kv)
+  st = stage(cfg, w, "bfloat16", page=16, cap=512)
+  n = 400
+  for at in sorted({0, keep - 1, keep, 63, 64, 65, 127, 128, 200, 399 - window, 400 - window} - {-1}):
+    if at < 0 or at >= n:
+      continue
+    ids = [(5 + 3 * i) % 48 + 2 for i in range(n)]
+    ids[at] = 1
+    ref = O.forward(cfg, w, ids)
+    before = st.counters()["tc_attention"]
+    whole = run(st, 0, ids, 0)
+    assert st.counters()["tc_attention"] == before + 1
+    st.release_slot(0)
+    assert rel(whole, ref) < TOL["bfloat16"], (at, "prompt")
+    got = torch.cat([run(st, 0, ids[:207], 0), run(st, 0, ids[207:], 207)])
+    st.release_slot(0)
+    assert rel(got, ref) < TOL["bfloat16"], (at, "two portions")
+    if keep <= at < n - window - 1:
+      inside, outside = ref[at + window - 1], ref[at + window]
+      assert float((inside - outside).abs().max()) > 5 * TOL["bfloat16"] * float(ref.abs().max())
+      assert rel(whole[at + window - 1: at + window + 1], ref[at + window - 1: at + window + 1]) < TOL["bfloat16"]
+  st.close()
+
+
+def test_bf16_prompt_kernels_equal_token_by_token(lib):
+  """bf16 serving: a 300-token prompt (tensor-core Linears and attention, tiled filters) against the same tokens one at a
+  time (split-K Linears, per-token attention, filters that write their own tails)."""
+  cfg = config([(delta(heads=2, kv=1, dim=64, vdim=32, conv=4), 256), (pair(heads=4, kv=2, dim=64, vdim=64, window=90, keep=4, r_heads=2, r_dim=48,
+                r_vdim=32), 256)], width=128, taps=4, side=16)
+  w = weights(cfg, seed=13)
+  ids = toks(300, cfg["vocab"], seed=14)
+  ref = O.forward(cfg, w, ids)
+  st = stage(cfg, w, "bfloat16", page=64)
+  whole = run(st, 0, ids, 0)
+  assert st.counters()["tc_attention"] == 1
+  st.release_slot(0)
+  run(st, 0, ids[:150], 0, rows=[])
+  single = torch.cat([run(st, 0, [t], 150 + i) for i, t in enumerate(ids[150:])])
+  st.close()
+  assert rel(whole, ref) < TOL["bfloat16"] and rel(single, ref[150:]) < TOL["bfloat16"]
+  assert rel(single, whole[150:]) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("lanes", ["4", "8", "16"])
+def test_recurrence_lanes_per_column(lib, monkeypatch, lanes):
+  """The recurrences spread a state column over 4, 8 or 16 lanes depending on the step's shape; every variant, pinned,
+  against the oracle: a prompt, portions, and single tokens, key dims that need padding and several chunks per lane."""
+  monkeypatch.setenv("XB_HY_LPC", lanes)
+  cfg = config([(delta(heads=3, kv=1, dim=24, vdim=20, conv=2), 0), (delta(heads=2, kv=2, dim=160, vdim=40, conv=3), 64),
+                (pair(ls=0.3, r_heads=5, r_dim=20, r_vdim=12), 0), (pair(r_heads=2, r_dim=136, r_vdim=70), 64)], width=96, taps=2, side=0)
+  w = weights(cfg, seed=21)
+  ids = toks(75, cfg["vocab"], seed=22)
+  ref = O.forward(cfg, w, ids)
+  st = stage(cfg, w, "float32")
+  whole = run(st, 0, ids, 0)
+  st.release_slot(0)
+  parts = torch.cat([run(st, 0, ids[:33], 0), run(st, 0, ids[33:35], 33)] + [run(st, 0, [t], 35 + i) for i, t in enumerate(ids[35:])])
+  st.close()
+  assert rel(whole, ref) < TOL["float32"] and rel(parts, ref) < TOL["float32"]
+
+
 # ----------------------------------------------------------------------------- the serving engine
 def test_greedy_generation_through_the_engine(lib, tmp_path):
   """B200ShardInferenceEngine (the plugin API the node drives: infer_prompt / sample / infer_tensor, its request table and

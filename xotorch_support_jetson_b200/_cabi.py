@@ -37,7 +37,7 @@ class ModelDesc(C.Structure):
   ]
 
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 def model_desc(**fields) -> ModelDesc:
@@ -86,6 +86,7 @@ class Counters(C.Structure):
   _fields_ = [
     ("launches", C.c_uint64), ("forwards", C.c_uint64), ("weight_bytes", C.c_uint64),
     ("kv_bytes_per_pos", C.c_uint64), ("kv_pages_total", C.c_uint64), ("kv_pages_free", C.c_uint64),
+    ("tc_attention", C.c_uint64),
   ]
 
 

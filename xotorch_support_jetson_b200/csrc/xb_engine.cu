@@ -848,6 +848,7 @@ static int launch_attn_g(xb_engine* e, const LayerW& w, const BatchMeta& m, int 
     // prefill: one block per (query tile, kv head), tcgen05 flash attention
     using Cfg = AttTcCfg<HD>;
     XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, G>), Cfg::SMEM_BYTES);
+    e->c.tc_attention++;
     XB_TRY(launch_k(e, xb_attn_prefill_tc_kernel<HD, G>, dim3(n_tiles, d.n_kv_heads), dim3(192), Cfg::SMEM_BYTES, st, 1, w.tmK,
                     w.tmV, e->q, m, m.tile_start, m.tile_len, e->attn, d.n_heads, d.n_kv_heads, scale_log2, AttMask{0, 0},
                     AttIo{(long long)d.n_heads * HD, nullptr, nullptr, 0}));

@@ -51,6 +51,7 @@ struct HyModel {
   std::vector<void*> allocs;
   bf16* t_head = nullptr;
   bool finalized = false;
+  int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
   int use_tc = 1;            // XB_HY_TC=0: every Linear through the plain kernels (A/B)
   size_t cap_P = 0, cap_m = 0, cap_head = 0;   // bytes of the Linear output buffers
   std::map<std::tuple<const void*, const void*, const void*, int>, GemmPlan> plans;
@@ -245,6 +246,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   {
     const char* g = getenv("XB_HY_TC");
     if (g != nullptr && g[0] == '0') hy->use_tc = 0;
+    const char* lp = getenv("XB_HY_LPC");
+    if (lp != nullptr && (atoi(lp) == 4 || atoi(lp) == 8 || atoi(lp) == 16)) hy->recur_lpc = atoi(lp);
   }
   XB_TRY(hy_alloc_t(hy, &hy->d_rows, R));
   XB_TRY(dmalloc((void**)&e->logits, R * (size_t)d.vocab * sizeof(float)));
@@ -464,24 +467,70 @@ static int hy_linear(xb_engine* e, const void* x, long long ldx, const bf16* w, 
   return 0;
 }
 
-// one recurrence launch: the instance with the fewest 16-row chunks per lane quad that cover the key dim
-template <bool DELTA>
-static int hy_recur(xb_engine* e, const RecurIn& in, float* state, long long ss, float* o, long long ldo, const BatchMeta& m, int n_seqs,
-                    int H, int dk, int dv, cudaStream_t st) {
-  const dim3 grid(n_seqs, H, (dv + HY_RC_COLS - 1) / HY_RC_COLS);
-#define HY_RECUR_CASE(NCH)                                                                                         \
-  if (dk <= 16 * NCH) {                                                                                            \
-    const size_t smem = (size_t)2 * HY_TS * (2 * 16 * NCH + HY_RC_COLS + 4) * sizeof(float);                       \
-    if (smem > 48 * 1024) XB_SMEM_ATTR_ONCE((hy_recur_kernel<NCH, DELTA>), smem);                                  \
-    return hy_launch(e, hy_recur_kernel<NCH, DELTA>, grid, dim3(128), smem, st, in, state, ss, o, ldo, m, H, dk, dv); \
+// one recurrence launch.  Lanes per state column: the fewest of 4, 8, 16 that still give two blocks per SM (one long
+// prompt wants many short chains, a batch of sequences few shuffles); then the fewest chunks per lane that cover the key dim.
+template <int LPC, bool DELTA>
+static int hy_recur_l(xb_engine* e, const RecurIn& in, float* state, long long ss, float* o, long long ldo, const BatchMeta& m,
+                      int n_seqs, int H, int dk, int dv, cudaStream_t st) {
+  constexpr int COLS = 128 / LPC;
+  const dim3 grid(n_seqs, H, (dv + COLS - 1) / COLS);
+#define HY_RECUR_CASE(NCH)                                                                                               \
+  if (dk <= 4 * LPC * NCH) {                                                                                             \
+    const size_t smem = (size_t)2 * HY_TS * (8 * LPC * NCH + COLS + 4) * sizeof(float);                                  \
+    if (smem > 48 * 1024) XB_SMEM_ATTR_ONCE((hy_recur_kernel<NCH, LPC, DELTA>), smem);                                   \
+    return hy_launch(e, hy_recur_kernel<NCH, LPC, DELTA>, grid, dim3(128), smem, st, in, state, ss, o, ldo, m, H, dk, dv); \
   }
   HY_RECUR_CASE(1)
   HY_RECUR_CASE(2)
   HY_RECUR_CASE(4)
-  HY_RECUR_CASE(8)
-  HY_RECUR_CASE(16)
+  if constexpr (LPC <= 8) { HY_RECUR_CASE(8) }
+  if constexpr (LPC <= 4) { HY_RECUR_CASE(16) }
 #undef HY_RECUR_CASE
   return xb_fail(1, "recurrent key dim %d exceeds %d", dk, HY_MAX_KDIM);
+}
+template <bool DELTA>
+static int hy_recur(xb_engine* e, const RecurIn& in, float* state, long long ss, float* o, long long ldo, const BatchMeta& m, int n_seqs,
+                    int H, int dk, int dv, cudaStream_t st) {
+  int lpc = e->hy->recur_lpc;
+  if (lpc == 0) {
+    const long long want = 2LL * e->num_sms;
+    lpc = 16;
+    if ((long long)n_seqs * H * ((dv + 31) / 32) >= want) lpc = 4;
+    else if ((long long)n_seqs * H * ((dv + 15) / 16) >= want) lpc = 8;
+  }
+  if (lpc == 4) return hy_recur_l<4, DELTA>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
+  if (lpc == 8) return hy_recur_l<8, DELTA>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
+  return hy_recur_l<16, DELTA>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
+}
+
+// causal per-channel filter over T rows (+ the slots' new tails): tap counts up to 4 through the tiled kernel, which in a
+// step of single tokens (no_span) also writes the tails; anything else through the general pair of kernels
+template <typename OT>
+static int hy_filter(xb_engine* e, int T, int n_seqs, bool no_span, const LinOut& in, int col0, int C, int taps, const float* w, float* tail,
+                     const BatchMeta& m, int identity, int act_silu, OT* out, long long ld_out, cudaStream_t st) {
+  const long long SS = (long long)e->hy->state_floats;
+  bool tail_done = false;
+  const dim3 tg((T + HY_TAPS_TT - 1) / HY_TAPS_TT, (C + 255) / 256);
+  const int wt = no_span ? 1 : 0;
+  switch (taps) {
+#define HY_TAPS_CASE(N)                                                                                                      \
+  case N:                                                                                                                    \
+    XB_TRY(hy_launch(e, hy_taps_tile_kernel<OT, N>, tg, dim3(256), 0, st, in, col0, C, w, tail, SS, m, identity, act_silu, wt, out, \
+                     ld_out, T));                                                                                            \
+    tail_done = no_span;                                                                                                     \
+    break;
+    HY_TAPS_CASE(1)
+    HY_TAPS_CASE(2)
+    HY_TAPS_CASE(3)
+    HY_TAPS_CASE(4)
+#undef HY_TAPS_CASE
+    default:
+      XB_TRY(hy_launch(e, hy_taps_kernel<OT>, dim3(T, (C + 255) / 256), dim3(256), 0, st, in, col0, C, taps, w, (const float*)tail, SS, m,
+                       identity, act_silu, out, ld_out));
+  }
+  if (taps > 1 && !tail_done)
+    XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (C + 255) / 256), dim3(256), 0, st, in, col0, C, taps, tail, SS, m));
+  return 0;
 }
 
 template <int HD, int GRP>
@@ -491,6 +540,7 @@ static int hy_attn_tc_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, int 
   XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, GRP>), Cfg::SMEM_BYTES);
   const AttMask mk{c.a_window, c.a_keep_first};
   const AttIo io{P.ld, P.bias != nullptr ? P.bias + l.off_q : nullptr, P.h + l.off_g, P.ld};
+  e->c.tc_attention++;
   return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP>, dim3(n_tiles, c.a_kv_heads), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV,
                    P.h + l.off_q, m, m.tile_start, m.tile_len, out, c.a_heads, c.a_kv_heads, c.a_scale * 1.4426950408889634f, mk, io);
 }
@@ -523,17 +573,11 @@ static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float 
 
 // what a sublayer reads: the normed stream plus its causal filter, as a Linear input; then the slot's new tail
 template <typename AT>
-static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, const float* w, size_t st_off, const BatchMeta& m, cudaStream_t st) {
+static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, bool no_span, const float* w, size_t st_off, const BatchMeta& m, cudaStream_t st) {
   HyModel* hy = e->hy;
-  const int D = hy->d.dim, taps = hy->d.taps;
-  const LinOut in = hy_plain(hy->hn, D);
-  float* tail = hy->state + st_off;
-  XB_TRY(hy_launch(e, hy_taps_kernel<AT>, dim3(T, (D + 255) / 256), dim3(256), 0, st, in, 0, D, taps, w, (const float*)tail,
-                   (long long)hy->state_floats, m, 1, 0, reinterpret_cast<AT*>(hy->a1), (long long)D));
-  if (taps > 1)
-    XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (D + 255) / 256), dim3(256), 0, st, in, 0, D, taps, tail,
-                     (long long)hy->state_floats, m));
-  return 0;
+  const int D = hy->d.dim;
+  return hy_filter<AT>(e, T, n_seqs, no_span, hy_plain(hy->hn, D), 0, D, hy->d.taps, w, hy->state + st_off, m, 1, 0,
+                       reinterpret_cast<AT*>(hy->a1), (long long)D, st);
 }
 
 template <typename AT>
@@ -550,6 +594,9 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
   m.page_tokens = e->page_tokens;
   const int D = d.dim;
   const long long SS = (long long)hy->state_floats;
+  const bool no_span = n_tiles == 0;   // a step of single tokens: no sequence spans two filter tiles
+  // few rows: the per-layer token input (two small Linears, gate, norm, residual) in one kernel, a block per row
+  const bool side_fused = T <= 64 && (size_t)(2 * D + d.side_dim) * sizeof(float) <= 48 * 1024;
   AT* a1 = reinterpret_cast<AT*>(hy->a1);
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
   XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab));
@@ -561,15 +608,12 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
     const bool has_ff = c.ff > 0, has_side = d.side_dim > 0;
     LinOut P, y1, y2 = hy_none();
     float s1 = 1.f, s2 = 0.f;
-    XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, l.canon1, l.st_canon1, m, st));
+    XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, no_span, l.canon1, l.st_canon1, m, st));
     XB_TRY(hy_linear<AT>(e, a1, D, l.w_in, l.t_in, l.b_in, T, l.n_in, D, hy->P, hy->cap_P, st, &P));
     if (c.mixer == XB_MIX_DELTA) {
       const int H = c.d_heads, G = c.d_kv_heads, dk = c.d_dim, dv = c.d_vdim, tp = c.d_taps;
       float* tail = hy->state + l.st_conv;
-      XB_TRY(hy_launch(e, hy_taps_kernel<float>, dim3(T, (l.c_conv + 255) / 256), dim3(256), 0, st, P, 0, l.c_conv, tp,
-                       (const float*)l.conv_w, (const float*)tail, SS, m, 0, 1, hy->c, (long long)l.c_conv));
-      if (tp > 1)
-        XB_TRY(hy_launch(e, hy_tail_update_kernel, dim3(n_seqs, (l.c_conv + 255) / 256), dim3(256), 0, st, P, 0, l.c_conv, tp, tail, SS, m));
+      XB_TRY(hy_filter<float>(e, T, n_seqs, no_span, P, 0, l.c_conv, tp, l.conv_w, tail, m, 0, 1, hy->c, (long long)l.c_conv, st));
       XB_TRY(hy_launch(e, hy_delta_prep_kernel, dim3(T), dim3(256), 0, st, hy->c, (long long)l.c_conv, P, l.off_b, l.off_a,
                        (const float*)l.A_log, (const float*)l.dt_bias, hy->beta, hy->decay, hy->qk, H, G, dk));
       {
@@ -617,17 +661,25 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
     }
     // x += norm1b(mixer); then whatever reads x next
     XB_TRY(hy_row_op<AT>(e, T, y1, s1, y2, s2, l.norm1b, 1.f, has_ff ? l.norm2 : (has_side ? nullptr : next_norm),
-                         (!has_ff && has_side) ? (void*)a1 : nullptr, st));
+                         (!has_ff && has_side && !side_fused) ? (void*)a1 : nullptr, st));
     if (has_ff) {
       LinOut u, dn;
-      XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, l.canon2, l.st_canon2, m, st));
+      XB_TRY(hy_sublayer_input<AT>(e, T, n_seqs, no_span, l.canon2, l.st_canon2, m, st));
       XB_TRY(hy_linear<AT>(e, a1, D, l.w_up, l.t_up, nullptr, T, c.ff, D, hy->P, hy->cap_P, st, &u));
       const long long n = (long long)T * c.ff;
-      XB_TRY(hy_launch(e, hy_relu2_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, u, a1, (long long)c.ff, T, c.ff));
+      if (std::is_same<AT, bf16>::value && u.h != nullptr && u.bias == nullptr && c.ff % 8 == 0 && u.ld % 8 == 0)
+        XB_TRY(hy_launch(e, hy_relu2_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, u.h, u.ld, reinterpret_cast<bf16*>(hy->a1),
+                         (long long)c.ff, T, c.ff));
+      else
+        XB_TRY(hy_launch(e, hy_relu2_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, u, a1, (long long)c.ff, T, c.ff));
       XB_TRY(hy_linear<AT>(e, a1, c.ff, l.w_down, l.t_down, nullptr, T, D, c.ff, hy->m1, hy->cap_m, st, &dn));
-      XB_TRY(hy_row_op<AT>(e, T, dn, 1.f, hy_none(), 0.f, l.norm2b, 1.f, has_side ? nullptr : next_norm, has_side ? (void*)a1 : nullptr, st));
+      XB_TRY(hy_row_op<AT>(e, T, dn, 1.f, hy_none(), 0.f, l.norm2b, 1.f, has_side ? nullptr : next_norm, (has_side && !side_fused) ? (void*)a1 : nullptr, st));
     }
-    if (has_side) {
+    if (has_side && side_fused) {
+      XB_TRY(hy_launch(e, hy_side_fused_kernel<AT>, dim3(T), dim3(1024), (size_t)(2 * D + d.side_dim) * sizeof(float), st, hy->x,
+                       (const int*)e->in_tokens, (const bf16*)hy->side_embed, (long long)d.side_dim * d.n_layers, li * d.side_dim, d.vocab,
+                       (const bf16*)l.w_sgate, (const bf16*)l.w_sproj, (const float*)l.side_norm, next_norm, hy->hn, d.norm_eps, D, d.side_dim));
+    } else if (has_side) {
       LinOut gt, yy;
       const int sd = d.side_dim;
       XB_TRY(hy_linear<AT>(e, a1, D, l.w_sgate, l.t_sgate, nullptr, T, sd, D, hy->P, hy->cap_P, st, &gt));

@@ -40,6 +40,9 @@ __device__ __forceinline__ float lin_at(const LinOut& o, long long row, int col)
 template <typename AT> __device__ __forceinline__ void act_store(AT* p, float v);
 template <> __device__ __forceinline__ void act_store<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void act_store<bf16>(bf16* p, float v) { *p = f2bf(v); }
+template <typename AT> __device__ __forceinline__ float2 act_load2(const AT* p);   // two neighbours; p 2-element aligned
+template <> __device__ __forceinline__ float2 act_load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 act_load2<bf16>(const bf16* p) { return bf2_to_f2(*reinterpret_cast<const uint32_t*>(p)); }
 template <typename AT> __device__ __forceinline__ float act_load(const AT* p);
 template <> __device__ __forceinline__ float act_load<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float act_load<bf16>(const bf16* p) { return bf2f(*p); }
@@ -164,6 +167,56 @@ __global__ void hy_taps_kernel(LinOut in, int col0, int C, int taps, const float
   }
   if (act_silu) acc = hy_silu(acc);
   act_store<OT>(out + (long long)row * ld_out + c, acc);
+}
+
+// The same filter with the tap count known at compile time: a thread owns a channel and walks HY_TAPS_TT consecutive token
+// rows with the last TAPS-1 inputs in registers, so weights and earlier inputs are read once per tile.  The window is
+// rebuilt (earlier rows of the step, the slot's tail, or zeros before position 0) at the tile's first row and wherever a
+// sequence begins.  write_tail (steps in which no sequence spans two tiles, e.g. one token per sequence): the thread that
+// holds a sequence's last row also leaves the slot's new tail, so hy_tail_update_kernel need not run.
+#define HY_TAPS_TT 16
+template <typename OT, int TAPS>
+__global__ void __launch_bounds__(256) hy_taps_tile_kernel(LinOut in, int col0, int C, const float* __restrict__ w, float* __restrict__ tail,
+                                                           long long tail_stride, BatchMeta m, int identity, int act_silu, int write_tail,
+                                                           OT* __restrict__ out, long long ld_out, int T) {
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int r0 = blockIdx.x * HY_TAPS_TT, r1 = r0 + HY_TAPS_TT < T ? r0 + HY_TAPS_TT : T;
+  float wv[TAPS];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) wv[j] = w[(long long)c * TAPS + j];
+  float win[TAPS];   // win[d - 1]: the input d steps back (TAPS - 1 used)
+#pragma unroll
+  for (int d = 0; d < TAPS; ++d) win[d] = 0.f;
+  for (int row = r0; row < r1; ++row) {
+    const int s = m.tok_seq[row];
+    const int start = s > 0 ? m.seq_last[s - 1] + 1 : 0;
+    float* tl = tail + (long long)m.seq_slot[s] * tail_stride;
+    if (row == r0 || row == start) {
+      const int pos = m.tok_pos[row], pos0 = m.tok_pos[start];
+#pragma unroll
+      for (int d = 1; d < TAPS; ++d) {
+        const int p = pos - d;
+        float v = 0.f;
+        if (p >= 0) v = row - d >= start ? lin_at(in, row - d, col0 + c) : tl[(long long)(p - (pos0 - (TAPS - 1))) * C + c];
+        win[d - 1] = v;
+      }
+    }
+    const float cur = lin_at(in, row, col0 + c);
+    float acc = identity ? cur : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) acc += wv[j] * win[TAPS - 2 - j];   // oldest first, as hy_taps_kernel
+    acc += wv[TAPS - 1] * cur;
+    if (act_silu) acc = hy_silu(acc);
+    act_store<OT>(out + (long long)row * ld_out + c, acc);
+#pragma unroll
+    for (int d = TAPS - 1; d >= 2; --d) win[d - 1] = win[d - 2];
+    win[0] = cur;
+    if (write_tail && row == m.seq_last[s]) {
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) tl[(long long)j * C + c] = win[TAPS - 2 - j];
+    }
+  }
 }
 
 // the slot's tail after this call: the last taps-1 inputs of the sequence, oldest first (runs after hy_taps_kernel)
@@ -322,14 +375,15 @@ __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ 
 //   delta rule: S_j <- g S_j;  u_j = beta (v_j - k . S_j);  S_j <- S_j + k u_j;  o_j = q . S_j
 //               with a = k . S_j and b = q . S_j taken on the OLD column: u_j = beta (v_j - g a), o_j = g b + (q . k) u_j
 //   HGRN2:      S_j <- f * S_j + (1 - f) v_j;  o_j = q . S_j      (f per row, in the k slot of the inputs)
-// Four lanes own one column: lane `sub` holds the rows of the 16-byte chunks sub, sub + 4, ... (NCH chunks, rows beyond
-// dk are zero), so a dot product over the rows ends in two shuffles and a warp carries 8 columns.  The 4 warps of a
-// block share (sequence, head) and 32 columns; the inputs of HY_TS steps (q, k or f, the block's v columns, and for the
-// delta rule beta, decay and q . k) arrive in shared memory by cp.async, one chunk of steps ahead of the arithmetic.
-// grid (n_seqs, H, ceil(dv / 32)), 128 threads; state [slot][H][dv][dk] fp32;
-// dynamic shared memory 2 * HY_TS * (2 * 16 * NCH + 36) floats.
+// LPC lanes (4, 8 or 16) own one column: lane `sub` holds the rows of the 16-byte chunks sub, sub + LPC, ... (NCH chunks,
+// rows beyond dk are zero), so a dot product over the rows ends in log2(LPC) shuffles and a warp carries 32 / LPC
+// columns.  More lanes per column mean more blocks and shorter per-step chains (one long sequence), fewer mean fewer
+// shuffles (many sequences).  The 4 warps of a block share (sequence, head) and 128 / LPC columns; the inputs of HY_TS
+// steps (q, k or f, the block's v columns, and for the delta rule beta, decay and q . k) arrive in shared memory by
+// cp.async, one chunk of steps ahead of the arithmetic.
+// grid (n_seqs, H, ceil(dv * LPC / 128)), 128 threads; state [slot][H][dv][dk] fp32;
+// dynamic shared memory 2 * HY_TS * (8 * LPC * NCH + 128 / LPC + 4) floats.
 #define HY_TS 16
-#define HY_RC_COLS 32
 struct RecurIn {
   const float* c;        // [T, ldc] prepared inputs
   long long ldc;
@@ -346,15 +400,16 @@ __device__ __forceinline__ void hy_cp16(float* dst, const float* src) {
 __device__ __forceinline__ void hy_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void hy_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int NCH, bool DELTA>
+template <int NCH, int LPC, bool DELTA>
 __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __restrict__ state, long long state_stride, float* __restrict__ o,
                                                        long long ldo, BatchMeta m, int H, int dk, int dv) {
   extern __shared__ __align__(16) float stg[];
-  constexpr int DKP = 16 * NCH;                 // padded key dim
+  constexpr int DKP = 4 * LPC * NCH;            // padded key dim
+  constexpr int HY_RC_COLS = 128 / LPC;         // columns of a block
   constexpr int STRIDE = 2 * DKP + HY_RC_COLS + 4;
   const int s = blockIdx.x, h = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 3;
-  const int j0 = blockIdx.z * HY_RC_COLS, jl = warp * 8 + (lane >> 2), j = j0 + jl;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & (LPC - 1);
+  const int j0 = blockIdx.z * HY_RC_COLS, jl = warp * (32 / LPC) + lane / LPC, j = j0 + jl;
   const bool live = j < dv;
   const int ncv = dv - j0 < HY_RC_COLS ? dv - j0 : HY_RC_COLS;
   const SeqSpan sp = seq_span(m, s);
@@ -372,7 +427,7 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
     const bool st_al = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(st) & 15) == 0;
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch) {
-      const int r = (ch * 4 + sub) * 4;
+      const int r = (ch * LPC + sub) * 4;
       if (have && st_al && r + 3 < dk) {
         const float4 v = *reinterpret_cast<const float4*>(st + r);
         S[4 * ch] = v.x; S[4 * ch + 1] = v.y; S[4 * ch + 2] = v.z; S[4 * ch + 3] = v.w;
@@ -433,7 +488,7 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
         float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
         for (int ch = 0; ch < NCH; ++ch) {
-          const int r = (ch * 4 + sub) * 4;
+          const int r = (ch * LPC + sub) * 4;
           const float4 q4 = *reinterpret_cast<const float4*>(sr + r);
           const float4 k4 = *reinterpret_cast<const float4*>(sr + DKP + r);
           kv[4 * ch] = k4.x; kv[4 * ch + 1] = k4.y; kv[4 * ch + 2] = k4.z; kv[4 * ch + 3] = k4.w;
@@ -443,8 +498,11 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
           b0 = fmaf(q4.z, S[4 * ch + 2], b0); b1 = fmaf(q4.w, S[4 * ch + 3], b1);
         }
         float a = a0 + a1, b = b0 + b1;
-        a += __shfl_xor_sync(0xffffffffu, a, 1); b += __shfl_xor_sync(0xffffffffu, b, 1);
-        a += __shfl_xor_sync(0xffffffffu, a, 2); b += __shfl_xor_sync(0xffffffffu, b, 2);
+#pragma unroll
+        for (int off = 1; off < LPC; off <<= 1) {
+          a += __shfl_xor_sync(0xffffffffu, a, off);
+          b += __shfl_xor_sync(0xffffffffu, b, off);
+        }
         const float be = sr[2 * DKP + HY_RC_COLS], gd = sr[2 * DKP + HY_RC_COLS + 1], qk = sr[2 * DKP + HY_RC_COLS + 2];
         const float u = be * (v - gd * a);
 #pragma unroll
@@ -454,7 +512,7 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
         float b0 = 0.f, b1 = 0.f;
 #pragma unroll
         for (int ch = 0; ch < NCH; ++ch) {
-          const int r = (ch * 4 + sub) * 4;
+          const int r = (ch * LPC + sub) * 4;
           const float4 q4 = *reinterpret_cast<const float4*>(sr + r);
           const float4 f4 = *reinterpret_cast<const float4*>(sr + DKP + r);
           S[4 * ch] = fmaf(f4.x, S[4 * ch], (1.0f - f4.x) * v);
@@ -465,8 +523,8 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
           b0 = fmaf(q4.z, S[4 * ch + 2], b0); b1 = fmaf(q4.w, S[4 * ch + 3], b1);
         }
         float b = b0 + b1;
-        b += __shfl_xor_sync(0xffffffffu, b, 1);
-        b += __shfl_xor_sync(0xffffffffu, b, 2);
+#pragma unroll
+        for (int off = 1; off < LPC; off <<= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
         if (sub == 0 && live) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = b;
       }
     }
@@ -476,7 +534,7 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
     const bool st_al = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(st) & 15) == 0;
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch) {
-      const int r = (ch * 4 + sub) * 4;
+      const int r = (ch * LPC + sub) * 4;
       if (st_al && r + 3 < dk) {
         *reinterpret_cast<float4*>(st + r) = make_float4(S[4 * ch], S[4 * ch + 1], S[4 * ch + 2], S[4 * ch + 3]);
       } else {
@@ -608,6 +666,9 @@ __global__ void __launch_bounds__(256) hy_attn_window_kernel(LinOut P, int off_q
   float acc[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  // even dv: a lane owns channel pairs (2 * (lane + 32 c), + 1), c < 4, and takes four keys per round so that their value
+  // loads are in flight together; odd dv: a lane owns channels lane + 32 c, one key per round
+  const bool pairs = (dv & 1) == 0;
   for (int base = warp * 32; base < n_vis; base += nw * 32) {
     const int idx = base + lane;
     float sc = -INFINITY;
@@ -626,23 +687,57 @@ __global__ void __launch_bounds__(256) hy_attn_window_kernel(LinOut P, int off_q
     for (int c = 0; c < 8; ++c) acc[c] *= corr;
     mx = nm;
     const int cnt = n_vis - base < 32 ? n_vis - base : 32;
-    for (int jj = 0; jj < cnt; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const long long pr = __shfl_sync(0xffffffffu, prow, jj);
-      const KT* vr = v_pool + pr * dv;
+    if (pairs) {
+      for (int jj = 0; jj < cnt; jj += 4) {   // lanes past cnt hold p = 0 and row 0 of the pool (finite values)
+        float pj[4];
+        float2 vv[4][4];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int d = lane + 32 * c;
-        if (d < dv) acc[c] = fmaf(pj, act_load<KT>(vr + d), acc[c]);
+        for (int u = 0; u < 4; ++u) {
+          pj[u] = __shfl_sync(0xffffffffu, p, jj + u);
+          const long long pr = __shfl_sync(0xffffffffu, prow, jj + u);
+          const KT* vr = v_pool + pr * dv;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int d = 2 * (lane + 32 * c);
+            vv[u][c] = (64 * c < dv && d < dv) ? act_load2<KT>(vr + d) : make_float2(0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (64 * c >= dv) continue;
+            acc[2 * c] = fmaf(pj[u], vv[u][c].x, acc[2 * c]);
+            acc[2 * c + 1] = fmaf(pj[u], vv[u][c].y, acc[2 * c + 1]);
+          }
+      }
+    } else {
+      for (int jj = 0; jj < cnt; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        const long long pr = __shfl_sync(0xffffffffu, prow, jj);
+        const KT* vr = v_pool + pr * dv;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int d = lane + 32 * c;
+          if (d < dv) acc[c] = fmaf(pj, act_load<KT>(vr + d), acc[c]);
+        }
       }
     }
   }
   float* mine = part + (long long)warp * (2 + dv);
   if (lane == 0) { mine[0] = mx; mine[1] = l; }
+  if (pairs) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const int d = lane + 32 * c;
-    if (d < dv) mine[2 + d] = acc[c];
+    for (int c = 0; c < 4; ++c) {
+      const int d = 2 * (lane + 32 * c);
+      if (d < dv) { mine[2 + d] = acc[2 * c]; mine[3 + d] = acc[2 * c + 1]; }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv) mine[2 + d] = acc[c];
+    }
   }
   __syncthreads();
   if (warp != 0) return;
@@ -684,6 +779,25 @@ __global__ void hy_relu2_kernel(LinOut u, AT* __restrict__ out, long long ld_out
   act_store<AT>(out + t * ld_out + i, v * v);
 }
 
+// the same on a bf16 matrix without bias, eight neighbours per thread (F, ld and ld_out multiples of 8)
+__global__ void hy_relu2_vec_kernel(const bf16* __restrict__ u, long long ld, bf16* __restrict__ out, long long ld_out, int T, int F) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int f8 = F >> 3;
+  if (idx >= (long long)T * f8) return;
+  const long long t = idx / f8;
+  const int i = (int)(idx - t * f8) << 3;
+  const uint4 v = *reinterpret_cast<const uint4*>(u + t * ld + i);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = bf2_to_f2(w[j]);
+    f.x = fmaxf(f.x, 0.f); f.y = fmaxf(f.y, 0.f);
+    r[j] = f2_to_bf2(f.x * f.x, f.y * f.y);
+  }
+  *reinterpret_cast<uint4*>(out + t * ld_out + i) = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 // g[t, i] = gelu_tanh(gate[t, i]) * side_embed[token[t], col0 + i]
 template <typename AT>
 __global__ void hy_side_gate_kernel(LinOut gate, const int* __restrict__ tokens, const bf16* __restrict__ side_embed, long long ld_se,
@@ -695,6 +809,61 @@ __global__ void hy_side_gate_kernel(LinOut gate, const int* __restrict__ tokens,
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
   act_store<AT>(out + t * ld_out + i, hy_gelu_tanh(lin_at(gate, t, i)) * bf2f(side_embed[(long long)tok * ld_se + col0 + i]));
+}
+
+// The whole per-layer token input for a few rows (decode steps), one block per row:
+//   g = gelu_tanh(W_gate xa) * side_embed[token, col0 ..];  y = W_proj g;  x += y / rms(y) * side_norm;  hn = norm(x) * (1 + nw)
+// with xa = x and g rounded to the activation type AT, as the separate Linears see them.  Dynamic smem (2 D + sd) floats.
+template <typename AT>
+__device__ __forceinline__ float act_round(float v);
+template <> __device__ __forceinline__ float act_round<float>(float v) { return v; }
+template <> __device__ __forceinline__ float act_round<bf16>(float v) { return bf2f(f2bf(v)); }
+template <typename AT>
+__global__ void __launch_bounds__(1024) hy_side_fused_kernel(float* __restrict__ x, const int* __restrict__ tokens, const bf16* __restrict__ side_embed,
+                                                             long long ld_se, int col0, int V, const bf16* __restrict__ w_gate,
+                                                             const bf16* __restrict__ w_proj, const float* __restrict__ side_norm,
+                                                             const float* __restrict__ nw, float* __restrict__ hn, float eps, int D, int sd) {
+  extern __shared__ float sm[];
+  __shared__ float red[32];
+  float* xs = sm;
+  float* ys = sm + D;
+  float* g = sm + 2 * D;
+  const long long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  float* xr = x + t * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) xs[i] = act_round<AT>(xr[i]);
+  __syncthreads();
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  for (int i = warp; i < sd; i += nwarps) {
+    const bf16* wr = w_gate + (long long)i * D;
+    float d = 0.f;
+    for (int k = lane; k < D; k += 32) d = fmaf(bf2f(wr[k]), xs[k], d);
+    d = warp_sum(d);
+    if (lane == 0) g[i] = act_round<AT>(hy_gelu_tanh(d) * bf2f(side_embed[(long long)tok * ld_se + col0 + i]));
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < D; j += blockDim.x) {
+    const bf16* wr = w_proj + (long long)j * sd;
+    float y = 0.f;
+    for (int i = 0; i < sd; ++i) y = fmaf(bf2f(wr[i]), g[i], y);
+    ys[j] = y;
+    ss += y * y;
+  }
+  ss = block_sum<1024>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+  float s2 = 0.f;
+  for (int j = threadIdx.x; j < D; j += blockDim.x) {
+    const float v = xr[j] + ys[j] * inv * side_norm[j];
+    xr[j] = v;
+    ys[j] = v;
+    s2 += v * v;
+  }
+  if (nw == nullptr) return;
+  s2 = block_sum<1024>(s2, red);
+  const float inv2 = 1.0f / sqrtf(s2 / (float)D + eps);
+  for (int j = threadIdx.x; j < D; j += blockDim.x) hn[t * D + j] = ys[j] * inv2 * (1.0f + nw[j]);
 }
 
 // rows idx[r] of the normed stream as the head's input
