@@ -51,6 +51,9 @@ struct HyModel {
   std::vector<void*> allocs;
   bf16* t_head = nullptr;
   bool finalized = false;
+  // steps of few rows are chains of short kernels: their launches overlap (programmatic serialization); prompts run long
+  // kernels, where blocks of the next kernel parked on the SMs cost more than the launch gap (measured: +17% per prompt)
+  bool pdl_now = false;
   int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
   int use_tc = 1;            // XB_HY_TC=0: every Linear through the plain kernels (A/B)
   size_t cap_P = 0, cap_m = 0, cap_head = 0;   // bytes of the Linear output buffers
@@ -409,6 +412,13 @@ static int hy_launch(xb_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  if (e->use_pdl && e->hy->pdl_now) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   XB_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
   e->c.launches++;
   return 0;
@@ -594,9 +604,10 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
   m.page_tokens = e->page_tokens;
   const int D = d.dim;
   const long long SS = (long long)hy->state_floats;
+  hy->pdl_now = T <= 128;
   const bool no_span = n_tiles == 0;   // a step of single tokens: no sequence spans two filter tiles
   // few rows: the per-layer token input (two small Linears, gate, norm, residual) in one kernel, a block per row
-  const bool side_fused = T <= 64 && (size_t)(2 * D + d.side_dim) * sizeof(float) <= 48 * 1024;
+  const bool side_fused = T <= 64 && (size_t)(2 * D + d.side_dim + 8) * sizeof(float) <= 48 * 1024;
   AT* a1 = reinterpret_cast<AT*>(hy->a1);
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
   XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab));
@@ -635,9 +646,9 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
         if (dk == 128) XB_TRY(hy_attn_tc<128>(e, l, m, n_tiles, P, reinterpret_cast<bf16*>(hy->a1), st));
         else XB_TRY(hy_attn_tc<64>(e, l, m, n_tiles, P, reinterpret_cast<bf16*>(hy->a1), st));
       } else {
-        // warps per (token, head): one per 64 visible keys, at most 8
+        // warps per (token, head): one per 64 visible keys, at most 16
         int aw = (c.a_window + c.a_keep_first + 63) / 64;
-        aw = aw < 1 ? 1 : (aw > 8 ? 8 : aw);
+        aw = aw < 1 ? 1 : (aw > 16 ? 16 : aw);
         const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dv)) * sizeof(float);
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT>, dim3(T, H), dim3(32 * aw), asm_bytes, st, P, l.off_q, l.off_g,
                          (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f, a1,
@@ -676,7 +687,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       XB_TRY(hy_row_op<AT>(e, T, dn, 1.f, hy_none(), 0.f, l.norm2b, 1.f, has_side ? nullptr : next_norm, (has_side && !side_fused) ? (void*)a1 : nullptr, st));
     }
     if (has_side && side_fused) {
-      XB_TRY(hy_launch(e, hy_side_fused_kernel<AT>, dim3(T), dim3(1024), (size_t)(2 * D + d.side_dim) * sizeof(float), st, hy->x,
+      XB_TRY(hy_launch(e, hy_side_fused_kernel<AT>, dim3(T), dim3(1024), (size_t)(2 * D + d.side_dim + 8) * sizeof(float), st, hy->x,
                        (const int*)e->in_tokens, (const bf16*)hy->side_embed, (long long)d.side_dim * d.n_layers, li * d.side_dim, d.vocab,
                        (const bf16*)l.w_sgate, (const bf16*)l.w_sproj, (const float*)l.side_norm, next_norm, hy->hn, d.norm_eps, D, d.side_dim));
     } else if (has_side) {

@@ -14,6 +14,9 @@
 #include "xb_kernels.cuh"
 #include <math.h>
 
+// Every kernel of the forward opens with griddepcontrol.launch_dependents / griddepcontrol.wait: launched with the
+// programmatic-serialization attribute, the next kernel's launch overlaps this one's execution and it touches upstream
+// data only after the wait (the whole chain of earlier kernels has then completed).
 #define HY_MAX_TAPS 16   // causal filters keep taps - 1 inputs per sequence
 #define HY_MAX_KDIM 256  // recurrent state: four lanes own one value column, up to 64 rows each
 
@@ -33,7 +36,12 @@ __device__ __forceinline__ float lin_at(const LinOut& o, long long row, int col)
   if (o.si.splits == 0) return *p + b;
   const int n = xb_n_segments(o.si, col);
   float s = 0.f;
-  for (int i = 0; i < n; ++i) s += p[i * o.plane];
+  int i = 0;
+  for (; i + 3 < n; i += 4) {   // four planes in flight
+    const float v0 = p[i * o.plane], v1 = p[(i + 1) * o.plane], v2 = p[(i + 2) * o.plane], v3 = p[(i + 3) * o.plane];
+    s += (v0 + v1) + (v2 + v3);
+  }
+  for (; i < n; ++i) s += p[i * o.plane];
   return s + b;
 }
 
@@ -67,6 +75,8 @@ __device__ __forceinline__ SeqSpan seq_span(const BatchMeta& m, int s) {
 
 // ----------------------------------------------------------------------------- embedding
 __global__ void hy_embed_kernel(const int* __restrict__ tokens, const bf16* __restrict__ emb, float* __restrict__ x, int D, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
@@ -93,6 +103,8 @@ struct RowOpArgs {
 
 template <typename AT, int NT>
 __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row[];
   __shared__ float red[32];
   const long long t = blockIdx.x;
@@ -148,6 +160,8 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
 template <typename OT>
 __global__ void hy_taps_kernel(LinOut in, int col0, int C, int taps, const float* __restrict__ w, const float* __restrict__ tail,
                                long long tail_stride, BatchMeta m, int identity, int act_silu, OT* __restrict__ out, long long ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -179,6 +193,8 @@ template <typename OT, int TAPS>
 __global__ void __launch_bounds__(256) hy_taps_tile_kernel(LinOut in, int col0, int C, const float* __restrict__ w, float* __restrict__ tail,
                                                            long long tail_stride, BatchMeta m, int identity, int act_silu, int write_tail,
                                                            OT* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const int r0 = blockIdx.x * HY_TAPS_TT, r1 = r0 + HY_TAPS_TT < T ? r0 + HY_TAPS_TT : T;
@@ -221,6 +237,8 @@ __global__ void __launch_bounds__(256) hy_taps_tile_kernel(LinOut in, int col0, 
 
 // the slot's tail after this call: the last taps-1 inputs of the sequence, oldest first (runs after hy_taps_kernel)
 __global__ void hy_tail_update_kernel(LinOut in, int col0, int C, int taps, float* __restrict__ tail, long long tail_stride, BatchMeta m) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int s = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -246,6 +264,8 @@ template <typename AT>
 __global__ void __launch_bounds__(256) hy_linear_small_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w,
                                                               const float* __restrict__ bias, float* __restrict__ y, long long ldy,
                                                               int T, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (n >= N) return;
@@ -289,6 +309,8 @@ template <typename AT>
 __global__ void __launch_bounds__(256) hy_linear_tiled_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w,
                                                               const float* __restrict__ bias, float* __restrict__ y, long long ldy,
                                                               int T, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float xs[16][68];
   __shared__ float ws[16][68];
   const int t0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
@@ -348,6 +370,8 @@ __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ 
                                                             const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                                             float* __restrict__ beta, float* __restrict__ decay, float* __restrict__ qk,
                                                             int H, int G, int dk) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   float* row = c + t * ldc;
@@ -403,6 +427,7 @@ template <int N> __device__ __forceinline__ void hy_cp_wait() { asm volatile("cp
 template <int NCH, int LPC, bool DELTA>
 __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __restrict__ state, long long state_stride, float* __restrict__ o,
                                                        long long ldo, BatchMeta m, int H, int dk, int dv) {
+  pdl_wait();   // no early trigger: this kernel runs long on few warps, and blocks of the next kernel parked beside them slow it
   extern __shared__ __align__(16) float stg[];
   constexpr int DKP = 4 * LPC * NCH;            // padded key dim
   constexpr int HY_RC_COLS = 128 / LPC;         // columns of a block
@@ -550,6 +575,8 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
 // Prep: q = silu(.), f = lower + (1 - lower) sigmoid(.), v copied, into one fp32 row [q | f | v].  grid (T, ceil(n / 256)).
 __global__ void hy_hgrn_prep_kernel(LinOut P, int off_q, int off_f, int off_v, const float* __restrict__ lower, float* __restrict__ c,
                                     long long ldc, int HK, int HV) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long t = blockIdx.x;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= 2 * HK + HV) return;
@@ -570,6 +597,8 @@ template <typename AT>
 __global__ void __launch_bounds__(256) hy_head_norm_kernel(const float* __restrict__ o, long long ldo, const float* __restrict__ w,
                                                            LinOut P, int off_gate, float eps, float scale, AT* __restrict__ out,
                                                            long long ld_out, int H, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int h = blockIdx.y * nw + warp; h < H; h += nw * gridDim.y) {
@@ -591,6 +620,8 @@ __global__ void __launch_bounds__(256) hy_head_norm_kernel(const float* __restri
 template <typename KT>
 __global__ void hy_kv_append_kernel(LinOut P, int off_k, int off_v, KT* __restrict__ k_pool, KT* __restrict__ v_pool, BatchMeta m,
                                     int G, int dk, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int s = m.tok_seq[row], pos = m.tok_pos[row];
   const int page = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
@@ -622,16 +653,25 @@ template <> __device__ __forceinline__ float hy_dot_row<float>(const float* __re
   }
   return d;
 }
+__device__ __forceinline__ float hy_dot8(const float* __restrict__ q, const uint4 u, float d) {
+  const float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), e = bf2_to_f2(u.w);
+  const float4 q0 = *reinterpret_cast<const float4*>(q), q1 = *reinterpret_cast<const float4*>(q + 4);
+  d = fmaf(q0.x, a.x, d); d = fmaf(q0.y, a.y, d); d = fmaf(q0.z, b.x, d); d = fmaf(q0.w, b.y, d);
+  d = fmaf(q1.x, c.x, d); d = fmaf(q1.y, c.y, d); d = fmaf(q1.z, e.x, d); d = fmaf(q1.w, e.y, d);
+  return d;
+}
 template <> __device__ __forceinline__ float hy_dot_row<bf16>(const float* __restrict__ q, const bf16* __restrict__ kr, int dk) {
   float d = 0.f;
   if ((dk & 7) == 0) {
-    for (int i = 0; i < dk; i += 8) {
-      const uint4 u = *reinterpret_cast<const uint4*>(kr + i);
-      const float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), e = bf2_to_f2(u.w);
-      const float4 q0 = *reinterpret_cast<const float4*>(q + i), q1 = *reinterpret_cast<const float4*>(q + i + 4);
-      d = fmaf(q0.x, a.x, d); d = fmaf(q0.y, a.y, d); d = fmaf(q0.z, b.x, d); d = fmaf(q0.w, b.y, d);
-      d = fmaf(q1.x, c.x, d); d = fmaf(q1.y, c.y, d); d = fmaf(q1.z, e.x, d); d = fmaf(q1.w, e.y, d);
+    int i = 0;
+    for (; i + 32 <= dk; i += 32) {   // four 16-byte loads in flight
+      const uint4 u0 = *reinterpret_cast<const uint4*>(kr + i), u1 = *reinterpret_cast<const uint4*>(kr + i + 8);
+      const uint4 u2 = *reinterpret_cast<const uint4*>(kr + i + 16), u3 = *reinterpret_cast<const uint4*>(kr + i + 24);
+      float d1 = hy_dot8(q + i + 8, u1, 0.f), d2 = hy_dot8(q + i + 16, u2, 0.f), d3 = hy_dot8(q + i + 24, u3, 0.f);
+      d = hy_dot8(q + i, u0, d);
+      d += (d1 + d2) + d3;
     }
+    for (; i < dk; i += 8) d = hy_dot8(q + i, *reinterpret_cast<const uint4*>(kr + i), d);
   } else {
     for (int i = 0; i < dk; ++i) d = fmaf(q[i], bf2f(kr[i]), d);
   }
@@ -645,10 +685,12 @@ template <> __device__ __forceinline__ float hy_dot_row<bf16>(const float* __res
 // mask only.  The epilogue multiplies by sigmoid(gate column) and `out_scale`.
 // dv <= 256.  Dynamic shared memory: (dk rounded up to 4) + warps * (2 + dv) floats.
 template <typename KT, typename AT>
-__global__ void __launch_bounds__(256) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
+__global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
                                                              const KT* __restrict__ v_pool, BatchMeta m, int H, int G, int dk, int dv,
                                                              int window, int keep_first, float scale, float out_scale,
                                                              AT* __restrict__ out, long long ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) float qsm[];
   const int row = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -771,6 +813,8 @@ __global__ void __launch_bounds__(256) hy_attn_window_kernel(LinOut P, int off_q
 // ----------------------------------------------------------------------------- feed-forward activation, side input, logits
 template <typename AT>
 __global__ void hy_relu2_kernel(LinOut u, AT* __restrict__ out, long long ld_out, int T, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * F) return;
   const long long t = idx / F;
@@ -781,6 +825,8 @@ __global__ void hy_relu2_kernel(LinOut u, AT* __restrict__ out, long long ld_out
 
 // the same on a bf16 matrix without bias, eight neighbours per thread (F, ld and ld_out multiples of 8)
 __global__ void hy_relu2_vec_kernel(const bf16* __restrict__ u, long long ld, bf16* __restrict__ out, long long ld_out, int T, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int f8 = F >> 3;
   if (idx >= (long long)T * f8) return;
@@ -802,6 +848,8 @@ __global__ void hy_relu2_vec_kernel(const bf16* __restrict__ u, long long ld, bf
 template <typename AT>
 __global__ void hy_side_gate_kernel(LinOut gate, const int* __restrict__ tokens, const bf16* __restrict__ side_embed, long long ld_se,
                                     int col0, int V, AT* __restrict__ out, long long ld_out, int T, int sd) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * sd) return;
   const long long t = idx / sd;
@@ -823,11 +871,13 @@ __global__ void __launch_bounds__(1024) hy_side_fused_kernel(float* __restrict__
                                                              long long ld_se, int col0, int V, const bf16* __restrict__ w_gate,
                                                              const bf16* __restrict__ w_proj, const float* __restrict__ side_norm,
                                                              const float* __restrict__ nw, float* __restrict__ hn, float eps, int D, int sd) {
-  extern __shared__ float sm[];
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float sm[];
   __shared__ float red[32];
-  float* xs = sm;
-  float* ys = sm + D;
-  float* g = sm + 2 * D;
+  float* g = sm;                        // sd floats, rounded up to a multiple of 4 (16-byte reads)
+  float* xs = sm + ((sd + 3) & ~3);
+  float* ys = xs + ((D + 3) & ~3);
   const long long t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   float* xr = x + t * D;
@@ -838,7 +888,11 @@ __global__ void __launch_bounds__(1024) hy_side_fused_kernel(float* __restrict__
   for (int i = warp; i < sd; i += nwarps) {
     const bf16* wr = w_gate + (long long)i * D;
     float d = 0.f;
-    for (int k = lane; k < D; k += 32) d = fmaf(bf2f(wr[k]), xs[k], d);
+    if ((D & 7) == 0) {
+      for (int k = lane * 8; k < D; k += 256) d = hy_dot8(xs + k, *reinterpret_cast<const uint4*>(wr + k), d);
+    } else {
+      for (int k = lane; k < D; k += 32) d = fmaf(bf2f(wr[k]), xs[k], d);
+    }
     d = warp_sum(d);
     if (lane == 0) g[i] = act_round<AT>(hy_gelu_tanh(d) * bf2f(side_embed[(long long)tok * ld_se + col0 + i]));
   }
@@ -847,7 +901,11 @@ __global__ void __launch_bounds__(1024) hy_side_fused_kernel(float* __restrict__
   for (int j = threadIdx.x; j < D; j += blockDim.x) {
     const bf16* wr = w_proj + (long long)j * sd;
     float y = 0.f;
-    for (int i = 0; i < sd; ++i) y = fmaf(bf2f(wr[i]), g[i], y);
+    if ((sd & 7) == 0) {
+      for (int i = 0; i < sd; i += 8) y = hy_dot8(g + i, *reinterpret_cast<const uint4*>(wr + i), y);
+    } else {
+      for (int i = 0; i < sd; ++i) y = fmaf(bf2f(wr[i]), g[i], y);
+    }
     ys[j] = y;
     ss += y * y;
   }
@@ -869,6 +927,8 @@ __global__ void __launch_bounds__(1024) hy_side_fused_kernel(float* __restrict__
 // rows idx[r] of the normed stream as the head's input
 template <typename AT>
 __global__ void hy_gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ idx, AT* __restrict__ dst, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* s = src + (long long)idx[r] * D;
   for (int i = threadIdx.x; i < D; i += blockDim.x) act_store<AT>(dst + (long long)r * D + i, s[i]);
@@ -876,6 +936,8 @@ __global__ void hy_gather_rows_kernel(const float* __restrict__ src, const int* 
 
 // logits <- cap * tanh(logits / cap) (cap > 0), from any Linear output into a dense fp32 [n, V]
 __global__ void hy_logits_kernel(LinOut y, float cap, float* __restrict__ out, int n, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)n * V) return;
   const long long t = idx / V;
