@@ -44,6 +44,9 @@ struct HyModel {
   float *x = nullptr, *hn = nullptr, *P = nullptr, *c = nullptr, *o = nullptr, *m1 = nullptr, *m2 = nullptr, *beta = nullptr,
         *decay = nullptr, *qk = nullptr, *head_raw = nullptr;
   void *a1 = nullptr, *a2 = nullptr, *head_in = nullptr;
+  bf16* qg = nullptr;        // [T, q | gate] of an attention layer for the tcgen05 kernel (see hy_qg_pack_kernel)
+  int* d_ones = nullptr;     // tile lengths of a step of single tokens
+  size_t maxQG = 0;
   int* d_rows = nullptr;
   size_t maxN = 0, maxK = 0, maxC = 0, maxO = 0, maxH = 1;
   std::map<std::string, HyTarget> names;
@@ -55,6 +58,7 @@ struct HyModel {
   // kernels, where blocks of the next kernel parked on the SMs cost more than the launch gap (measured: +17% per prompt)
   bool pdl_now = false;
   int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
+  int use_tc_attn = 1;       // XB_HY_TC_ATTN=0: attention through the per-token kernel everywhere (A/B)
   int use_tc = 1;            // XB_HY_TC=0: every Linear through the plain kernels (A/B)
   size_t cap_P = 0, cap_m = 0, cap_head = 0;   // bytes of the Linear output buffers
   std::map<std::tuple<const void*, const void*, const void*, int>, GemmPlan> plans;
@@ -182,6 +186,7 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       hy_name_vec(hy, p + "mix.right.norm", l.head_norm, rv);
       hy_name_rows(hy, p + "mix.right.o", l.w_o2, 0, D, l.n_o2);
       l.tc_attn = !d.compute_fp32 && dk == dv && (dk == 64 || dk == 128) && H / G <= 8 && c.a_scale > 0.f;
+      if (l.tc_attn && (size_t)(H * (dk + dv)) > hy->maxQG) hy->maxQG = H * (dk + dv);
       l.st_rec = st; st += (size_t)(Hr * rv * rk);
       const size_t cc = (size_t)(2 * Hr * rk + Hr * rv);
       if (cc > hy->maxC) hy->maxC = cc;
@@ -249,10 +254,18 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   {
     const char* g = getenv("XB_HY_TC");
     if (g != nullptr && g[0] == '0') hy->use_tc = 0;
+    const char* ta = getenv("XB_HY_TC_ATTN");
+    if (ta != nullptr && ta[0] == '0') hy->use_tc_attn = 0;
     const char* lp = getenv("XB_HY_LPC");
     if (lp != nullptr && (atoi(lp) == 4 || atoi(lp) == 8 || atoi(lp) == 16)) hy->recur_lpc = atoi(lp);
   }
   XB_TRY(hy_alloc_t(hy, &hy->d_rows, R));
+  if (hy->maxQG > 0) {
+    XB_TRY(hy_alloc_t(hy, &hy->qg, Tm * hy->maxQG));
+    std::vector<int> ones((size_t)d.max_seqs, 1);
+    XB_TRY(hy_alloc_t(hy, &hy->d_ones, (size_t)d.max_seqs));
+    XB_CUDA(cudaMemcpy(hy->d_ones, ones.data(), ones.size() * sizeof(int), cudaMemcpyHostToDevice));
+  }
   XB_TRY(dmalloc((void**)&e->logits, R * (size_t)d.vocab * sizeof(float)));
   e->c.weight_bytes = wbytes;
   e->c.kv_bytes_per_pos = kvpos;
@@ -543,28 +556,33 @@ static int hy_filter(xb_engine* e, int T, int n_seqs, bool no_span, const LinOut
   return 0;
 }
 
+struct HyAttnIn {
+  const bf16* q;             // q rows, pitch io.ldq
+  AttIo io;
+  const int *tile_start, *tile_len;
+  int n_tiles;
+};
 template <int HD, int GRP>
-static int hy_attn_tc_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, int n_tiles, const LinOut& P, bf16* out, cudaStream_t st) {
+static int hy_attn_tc_g(xb_engine* e, const HyLayer& l, const BatchMeta& m, const HyAttnIn& in, bf16* out, cudaStream_t st) {
   using Cfg = AttTcCfg<HD>;
   const xb_hybrid_layer& c = l.d;
   XB_SMEM_ATTR_ONCE((xb_attn_prefill_tc_kernel<HD, GRP>), Cfg::SMEM_BYTES);
   const AttMask mk{c.a_window, c.a_keep_first};
-  const AttIo io{P.ld, P.bias != nullptr ? P.bias + l.off_q : nullptr, P.h + l.off_g, P.ld};
   e->c.tc_attention++;
-  return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP>, dim3(n_tiles, c.a_kv_heads), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV,
-                   P.h + l.off_q, m, m.tile_start, m.tile_len, out, c.a_heads, c.a_kv_heads, c.a_scale * 1.4426950408889634f, mk, io);
+  return hy_launch(e, xb_attn_prefill_tc_kernel<HD, GRP>, dim3(in.n_tiles, c.a_kv_heads), dim3(192), Cfg::SMEM_BYTES, st, l.tmK, l.tmV,
+                   in.q, m, in.tile_start, in.tile_len, out, c.a_heads, c.a_kv_heads, c.a_scale * 1.4426950408889634f, mk, in.io);
 }
 template <int HD>
-static int hy_attn_tc(xb_engine* e, const HyLayer& l, const BatchMeta& m, int n_tiles, const LinOut& P, bf16* out, cudaStream_t st) {
+static int hy_attn_tc(xb_engine* e, const HyLayer& l, const BatchMeta& m, const HyAttnIn& in, bf16* out, cudaStream_t st) {
   switch (l.d.a_heads / l.d.a_kv_heads) {
-    case 1: return hy_attn_tc_g<HD, 1>(e, l, m, n_tiles, P, out, st);
-    case 2: return hy_attn_tc_g<HD, 2>(e, l, m, n_tiles, P, out, st);
-    case 3: return hy_attn_tc_g<HD, 3>(e, l, m, n_tiles, P, out, st);
-    case 4: return hy_attn_tc_g<HD, 4>(e, l, m, n_tiles, P, out, st);
-    case 5: return hy_attn_tc_g<HD, 5>(e, l, m, n_tiles, P, out, st);
-    case 6: return hy_attn_tc_g<HD, 6>(e, l, m, n_tiles, P, out, st);
-    case 7: return hy_attn_tc_g<HD, 7>(e, l, m, n_tiles, P, out, st);
-    case 8: return hy_attn_tc_g<HD, 8>(e, l, m, n_tiles, P, out, st);
+    case 1: return hy_attn_tc_g<HD, 1>(e, l, m, in, out, st);
+    case 2: return hy_attn_tc_g<HD, 2>(e, l, m, in, out, st);
+    case 3: return hy_attn_tc_g<HD, 3>(e, l, m, in, out, st);
+    case 4: return hy_attn_tc_g<HD, 4>(e, l, m, in, out, st);
+    case 5: return hy_attn_tc_g<HD, 5>(e, l, m, in, out, st);
+    case 6: return hy_attn_tc_g<HD, 6>(e, l, m, in, out, st);
+    case 7: return hy_attn_tc_g<HD, 7>(e, l, m, in, out, st);
+    case 8: return hy_attn_tc_g<HD, 8>(e, l, m, in, out, st);
   }
   return xb_fail(1, "no tcgen05 attention for %d query heads per key head", l.d.a_heads / l.d.a_kv_heads);
 }
@@ -605,7 +623,7 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
   const int D = d.dim;
   const long long SS = (long long)hy->state_floats;
   hy->pdl_now = T <= 128;
-  const bool no_span = n_tiles == 0;   // a step of single tokens: no sequence spans two filter tiles
+  const bool no_span = T == n_seqs;    // a step of single tokens: no sequence spans two filter tiles
   // few rows: the per-layer token input (two small Linears, gate, norm, residual) in one kernel, a block per row
   const bool side_fused = T <= 64 && (size_t)(2 * D + d.side_dim + 8) * sizeof(float) <= 48 * 1024;
   AT* a1 = reinterpret_cast<AT*>(hy->a1);
@@ -640,11 +658,27 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
       const int Hr = c.r_heads, rk = c.r_dim, rv = c.r_vdim;
       XB_TRY(hy_launch(e, hy_kv_append_kernel<KT>, dim3(T, (G * (dk + dv) + 255) / 256), dim3(256), 0, st, P, l.off_k, l.off_v, (KT*)l.k_pool, (KT*)l.v_pool, m, G, dk, dv));
-      // a prompt's portion whose projection came back as a bf16 matrix: the tcgen05 kernel (16-byte loads of q and gate rows)
-      const bool tc = std::is_same<AT, bf16>::value && l.tc_attn && n_tiles > 0 && P.h != nullptr && P.ld % 8 == 0 && l.off_g % 8 == 0;
+      // bf16 serving at the head sizes it takes: the tcgen05 kernel, over the step's query tiles (a step of single tokens:
+      // one tile per sequence).  It reads q and the gate as bf16 rows: straight from the projection when that came back
+      // as a bf16 matrix (16-byte loads need aligned pitches), else from a packed copy of the split-K planes.
+      const bool single = T == n_seqs;
+      const bool tc = std::is_same<AT, bf16>::value && l.tc_attn && hy->use_tc_attn && (n_tiles > 0 || single);
       if (tc) {
-        if (dk == 128) XB_TRY(hy_attn_tc<128>(e, l, m, n_tiles, P, reinterpret_cast<bf16*>(hy->a1), st));
-        else XB_TRY(hy_attn_tc<64>(e, l, m, n_tiles, P, reinterpret_cast<bf16*>(hy->a1), st));
+        HyAttnIn in;
+        in.tile_start = n_tiles > 0 ? m.tile_start : m.tok_seq;   // single tokens: row i is sequence i
+        in.tile_len = n_tiles > 0 ? m.tile_len : hy->d_ones;
+        in.n_tiles = n_tiles > 0 ? n_tiles : n_seqs;
+        if (P.h != nullptr && P.ld % 8 == 0 && l.off_g % 8 == 0) {
+          in.q = P.h + l.off_q;
+          in.io = AttIo{P.ld, P.bias != nullptr ? P.bias + l.off_q : nullptr, P.h + l.off_g, P.ld};
+        } else {
+          const int nq = H * dk, ng = H * dv;
+          XB_TRY(hy_launch(e, hy_qg_pack_kernel, dim3(T, (nq + ng + 255) / 256), dim3(256), 0, st, P, l.off_q, nq, l.off_g, ng, hy->qg));
+          in.q = hy->qg;
+          in.io = AttIo{(long long)(nq + ng), nullptr, hy->qg + nq, (long long)(nq + ng)};
+        }
+        if (dk == 128) XB_TRY(hy_attn_tc<128>(e, l, m, in, reinterpret_cast<bf16*>(hy->a1), st));
+        else XB_TRY(hy_attn_tc<64>(e, l, m, in, reinterpret_cast<bf16*>(hy->a1), st));
       } else {
         // warps per (token, head): one per 64 visible keys, at most 16
         int aw = (c.a_window + c.a_keep_first + 63) / 64;

@@ -678,6 +678,17 @@ template <> __device__ __forceinline__ float hy_dot_row<bf16>(const float* __res
   return d;
 }
 
+// q (bias added) and the output gate of the attention heads as one bf16 row [q | gate] per token: what the tcgen05 attention
+// reads when the projection came back as split-K planes (steps of few rows).  grid (T, ceil((nq + ng) / 256)).
+__global__ void hy_qg_pack_kernel(LinOut P, int off_q, int nq, int off_g, int ng, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= nq + ng) return;
+  out[t * (nq + ng) + i] = f2bf(lin_at(P, t, i < nq ? off_q + i : off_g + (i - nq)));
+}
+
 // One block per (token, query head); its warps split the visible keys 32 at a time.  Query i sees key j when j <= i and
 // (i - j < window or j < keep_first): the kept first keys, then the window.  In a 32-key tile a lane scores one key (fp32
 // dot with the query in shared memory), the warp does the online softmax, then lanes own value channels for the weighted
