@@ -133,7 +133,7 @@ def test_cabi_exports_every_declared_symbol(built_lib):
   body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
   fields = [n.strip() for decl in re.findall(r"(?:u?int32_t|float)\s+([^;]+);", body) for n in decl.split(",")]
   assert fields == [n for n, _ in _cabi.ModelDesc._fields_]
-  assert ctypes.sizeof(_cabi.ModelDesc) == 20 * 4 and ctypes.sizeof(_cabi.Counters) == 6 * 8
+  assert ctypes.sizeof(_cabi.ModelDesc) == 20 * 4 and ctypes.sizeof(_cabi.Counters) == 7 * 8
   assert _cabi.model_desc(n_layers=1).struct_size == 80
 
 
