@@ -533,14 +533,19 @@ static int hy_filter(xb_engine* e, int T, int n_seqs, bool no_span, const LinOut
                      const BatchMeta& m, int identity, int act_silu, OT* out, long long ld_out, cudaStream_t st) {
   const long long SS = (long long)e->hy->state_floats;
   bool tail_done = false;
-  const dim3 tg((T + HY_TAPS_TT - 1) / HY_TAPS_TT, (C + 255) / 256);
+  const bool few = T <= 64;   // a block per row instead of 16 rows per thread
+  const dim3 tg(few ? T : (T + 15) / 16, (C + 255) / 256);
   const int wt = no_span ? 1 : 0;
   switch (taps) {
-#define HY_TAPS_CASE(N)                                                                                                      \
-  case N:                                                                                                                    \
-    XB_TRY(hy_launch(e, hy_taps_tile_kernel<OT, N>, tg, dim3(256), 0, st, in, col0, C, w, tail, SS, m, identity, act_silu, wt, out, \
-                     ld_out, T));                                                                                            \
-    tail_done = no_span;                                                                                                     \
+#define HY_TAPS_CASE(N)                                                                                                          \
+  case N:                                                                                                                        \
+    if (few)                                                                                                                     \
+      XB_TRY(hy_launch(e, hy_taps_tile_kernel<OT, N, 1>, tg, dim3(256), 0, st, in, col0, C, w, tail, SS, m, identity, act_silu, wt, out, \
+                       ld_out, T));                                                                                              \
+    else                                                                                                                         \
+      XB_TRY(hy_launch(e, hy_taps_tile_kernel<OT, N, 16>, tg, dim3(256), 0, st, in, col0, C, w, tail, SS, m, identity, act_silu, wt, out, \
+                       ld_out, T));                                                                                              \
+    tail_done = no_span;                                                                                                         \
     break;
     HY_TAPS_CASE(1)
     HY_TAPS_CASE(2)

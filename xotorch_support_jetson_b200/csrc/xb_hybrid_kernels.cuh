@@ -183,13 +183,13 @@ __global__ void hy_taps_kernel(LinOut in, int col0, int C, int taps, const float
   act_store<OT>(out + (long long)row * ld_out + c, acc);
 }
 
-// The same filter with the tap count known at compile time: a thread owns a channel and walks HY_TAPS_TT consecutive token
-// rows with the last TAPS-1 inputs in registers, so weights and earlier inputs are read once per tile.  The window is
-// rebuilt (earlier rows of the step, the slot's tail, or zeros before position 0) at the tile's first row and wherever a
-// sequence begins.  write_tail (steps in which no sequence spans two tiles, e.g. one token per sequence): the thread that
-// holds a sequence's last row also leaves the slot's new tail, so hy_tail_update_kernel need not run.
-#define HY_TAPS_TT 16
-template <typename OT, int TAPS>
+// The same filter with the tap count known at compile time: a thread owns a channel and walks TT consecutive token rows
+// with the last TAPS-1 inputs in registers, so weights and earlier inputs are read once per tile (TT = 16 for prompts; TT = 1
+// gives steps of few rows a block per row).  A sequence ends where the next row belongs to another.  The window is rebuilt (earlier rows of the step, the
+// slot's tail, or zeros before position 0) at the tile's first row and wherever a sequence begins.  write_tail (steps in
+// which no sequence spans two tiles, e.g. one token per sequence): the thread that holds a sequence's last row also
+// leaves the slot's new tail, so hy_tail_update_kernel need not run.
+template <typename OT, int TAPS, int TT>
 __global__ void __launch_bounds__(256) hy_taps_tile_kernel(LinOut in, int col0, int C, const float* __restrict__ w, float* __restrict__ tail,
                                                            long long tail_stride, BatchMeta m, int identity, int act_silu, int write_tail,
                                                            OT* __restrict__ out, long long ld_out, int T) {
@@ -197,18 +197,27 @@ __global__ void __launch_bounds__(256) hy_taps_tile_kernel(LinOut in, int col0, 
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  const int r0 = blockIdx.x * HY_TAPS_TT, r1 = r0 + HY_TAPS_TT < T ? r0 + HY_TAPS_TT : T;
+  const int r0 = blockIdx.x * TT;
+  const int last_row = (r0 + TT < T ? r0 + TT : T) - 1;
+  // most tiles lie inside one sequence (rows of a sequence are contiguous): then no row asks again
+  const int s_first = m.tok_seq[r0], s_last = m.tok_seq[last_row];
+  const int s_next = last_row + 1 < T ? m.tok_seq[last_row + 1] : -1;
+  const bool uniform = s_first == s_last;
   float wv[TAPS];
 #pragma unroll
   for (int j = 0; j < TAPS; ++j) wv[j] = w[(long long)c * TAPS + j];
   float win[TAPS];   // win[d - 1]: the input d steps back (TAPS - 1 used)
 #pragma unroll
   for (int d = 0; d < TAPS; ++d) win[d] = 0.f;
-  for (int row = r0; row < r1; ++row) {
-    const int s = m.tok_seq[row];
-    const int start = s > 0 ? m.seq_last[s - 1] + 1 : 0;
-    float* tl = tail + (long long)m.seq_slot[s] * tail_stride;
-    if (row == r0 || row == start) {
+#pragma unroll
+  for (int i = 0; i < TT; ++i) {
+    const int row = r0 + i;
+    if (row > last_row) break;
+    const int s = uniform ? s_first : m.tok_seq[row];
+    const bool begins = !uniform && i > 0 && m.tok_seq[row - 1] != s;
+    if (i == 0 || begins) {
+      const float* tl = tail + (long long)m.seq_slot[s] * tail_stride;
+      const int start = begins ? row : (s > 0 ? m.seq_last[s - 1] + 1 : 0);
       const int pos = m.tok_pos[row], pos0 = m.tok_pos[start];
 #pragma unroll
       for (int d = 1; d < TAPS; ++d) {
@@ -228,7 +237,8 @@ __global__ void __launch_bounds__(256) hy_taps_tile_kernel(LinOut in, int col0, 
 #pragma unroll
     for (int d = TAPS - 1; d >= 2; --d) win[d - 1] = win[d - 2];
     win[0] = cur;
-    if (write_tail && row == m.seq_last[s]) {
+    if (write_tail && (row == last_row ? s_next != s : (!uniform && m.tok_seq[row + 1] != s))) {
+      float* tl = tail + (long long)m.seq_slot[s] * tail_stride;
 #pragma unroll
       for (int j = 0; j < TAPS - 1; ++j) tl[(long long)j * C + c] = win[TAPS - 2 - j];
     }
