@@ -515,7 +515,8 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
     else hy_cp_wait<0>();
     __syncthreads();
     const float* buf = stg + cur * HY_TS * STRIDE;
-    for (int ts = 0; ts < nt; ++ts) {
+    const long long orow0 = (long long)(sp.start + t0) * ldo + (long long)h * dv + j;
+    auto step = [&](int ts) {
       const float* sr = buf + ts * STRIDE;
       const float v = sr[2 * DKP + jl];
       if (DELTA) {
@@ -542,7 +543,7 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
         const float u = be * (v - gd * a);
 #pragma unroll
         for (int i = 0; i < 4 * NCH; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
-        if (sub == 0 && live) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = fmaf(qk, u, gd * b);
+        if (sub == 0 && live) o[orow0 + (long long)ts * ldo] = fmaf(qk, u, gd * b);
       } else {
         float b0 = 0.f, b1 = 0.f;
 #pragma unroll
@@ -560,8 +561,16 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
         float b = b0 + b1;
 #pragma unroll
         for (int off = 1; off < LPC; off <<= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
-        if (sub == 0 && live) o[(long long)(sp.start + t0 + ts) * ldo + (long long)h * dv + j] = b;
+        if (sub == 0 && live) o[orow0 + (long long)ts * ldo] = b;
       }
+    };
+    // full chunks: unrolled, so that the loads and reductions of neighbouring steps overlap (HGRN2's steps depend on one
+    // another through a single FMA per row; the delta rule's through the whole a -> u -> S chain, so less is gained)
+    if (nt == HY_TS) {
+#pragma unroll 4
+      for (int ts = 0; ts < HY_TS; ++ts) step(ts);
+    } else {
+      for (int ts = 0; ts < nt; ++ts) step(ts);
     }
     __syncthreads();   // the buffer is refilled by the next iteration's copies
   }
