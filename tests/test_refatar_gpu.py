@@ -376,3 +376,43 @@ def test_greedy_generation_through_the_engine(lib, tmp_path):
     if float(top2[0] - top2[1]) > 1e-3:
       assert tok == int(ref.argmax()), step
     seq.append(tok)
+
+
+# ----------------------------------------------------------------------------- the command line
+def test_trace_runner_replays_steps(lib, tmp_path):
+  """bin/trace_run as a user calls it: a model folder (config.json + one safetensors file), steps on standard input -- a
+  whole prompt, a prompt in portions with single tokens behind it, a request that ends and whose slot the next one takes --
+  and <step>.f32 files with the rows that were asked for, in the order asked, against the oracle."""
+  import json
+  import subprocess
+  import sys
+  from pathlib import Path
+  from safetensors.torch import save_file
+  cfg = config([(pair(heads=6, kv=3, dim=64, vdim=64, window=20, keep=2, r_heads=3, r_dim=24, r_vdim=40), 96), (delta(), 0)], width=64,
+               vocab=120, taps=2, side=4, softcap=8.0)
+  w = weights(cfg, seed=17)
+  model = tmp_path / "model"
+  model.mkdir()
+  (model / "config.json").write_text(json.dumps(cfg))
+  save_file({k: v.contiguous() for k, v in w.items()}, str(model / "model.safetensors"))
+  a, b = toks(50, cfg["vocab"], 41), toks(31, cfg["vocab"], 42)
+  steps = [
+    {"step": 0, "entries": [{"id": "a", "tokens": a, "want": [49, 0, 20]}], "end": ["a"]},
+    {"step": 1, "entries": [{"id": "b", "tokens": b[:17], "want": []}], "end": []},
+    {"step": 2, "entries": [{"id": "b", "tokens": b[17:19], "want": [0, 1]}], "end": []},
+  ] + [{"step": 3 + i, "entries": [{"id": "b", "tokens": [t], "want": [0]}], "end": (["b"] if 19 + i == len(b) - 1 else [])}
+       for i, t in enumerate(b[19:])]
+  root = Path(__file__).resolve().parent.parent
+  ra, rb = O.forward(cfg, w, a), O.forward(cfg, w, b)
+  for dtype in ("float32", "bfloat16"):
+    out = tmp_path / f"out_{dtype}"
+    p = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    rd = lambda i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"])).double()  # noqa: E731
+    assert rel(rd(0), ra[[49, 0, 20]]) < TOL[dtype]
+    assert not (out / "1.f32").exists()
+    assert rel(rd(2), rb[17:19]) < TOL[dtype]
+    got = torch.cat([rd(3 + i) for i in range(len(b) - 19)])
+    assert rel(got, rb[19:]) < TOL[dtype]
