@@ -256,26 +256,27 @@ def test_far_key_among_hundreds_in_kept_first(lib):
 
 
 # ----------------------------------------------------------------------------- bf16 serving kernels
-def planted64(window, keep, heads=6, kv=2):
-  """planted() at the head sizes the tensor-core prompt attention takes (key and value heads of 64), bf16 weights."""
-  cfg = config([(pair(heads=heads, kv=kv, dim=64, vdim=64, window=window, keep=keep, rs=0.0, ls=1.0, scale=1.0), 0)], width=128, vocab=50,
+def planted64(window, keep, heads=6, kv=2, hd=64):
+  """planted() at the head sizes the tensor-core prompt attention takes (key and value heads of 64 or 128), bf16 weights."""
+  cfg = config([(pair(heads=heads, kv=kv, dim=hd, vdim=hd, window=window, keep=keep, rs=0.0, ls=1.0, scale=1.0), 0)], width=128, vocab=50,
                taps=0, side=0, softcap=0)
   w = {k: v.float() for k, v in weights(cfg, seed=9).items()}
   w["embed"][1] *= 0.0
   w["embed"][1, 0] = 6.0
   w["l0.mix.left.k"][:, 0] = 0.0
-  w["l0.mix.left.k"][0::64, 0] = 3.0
-  w["l0.mix.left.q.b"][0::64] = 4.0
+  w["l0.mix.left.k"][0::hd, 0] = 3.0
+  w["l0.mix.left.q.b"][0::hd] = 4.0
   w["l0.mix.left.v"][:, 0] = 2.0
   return cfg, {k: v.to(torch.bfloat16) for k, v in w.items()}
 
 
-@pytest.mark.parametrize("window,keep,heads,kv", [(100, 5, 6, 2), (64, 0, 4, 4), (70, 66, 8, 1), (1, 0, 2, 1)])
-def test_tensor_core_prompt_attention_edges(lib, window, keep, heads, kv):
+@pytest.mark.parametrize("window,keep,heads,kv,hd", [(100, 5, 6, 2, 64), (64, 0, 4, 4, 64), (70, 66, 8, 1, 64), (1, 0, 2, 1, 64),
+                                                     (130, 1, 5, 1, 128), (33, 3, 7, 7, 128)])
+def test_tensor_core_prompt_attention_edges(lib, window, keep, heads, kv, hd):
   """Prompts long enough for the bf16 projections to come back as matrices run the tcgen05 attention: 64-key tiles are
   visited through the kept-first / window map, so the planted key sits at tile borders, at the window's two edges and
   among the kept first keys, in a whole prompt and in a second portion that starts far from position 0."""
-  cfg, w = planted64(window, keep, heads, kv)
+  cfg, w = planted64(window, keep, heads, kv, hd)
   st = stage(cfg, w, "bfloat16", page=16, cap=512)
   n = 400
   for at in sorted({0, keep - 1, keep, 63, 64, 65, 127, 128, 200, 399 - window, 400 - window} - {-1}):
