@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XB_ABI_VERSION 5
+#define XB_ABI_VERSION 6
 
 typedef struct xb_engine xb_engine;
 
@@ -217,11 +217,30 @@ enum {
   XB_MIX_DELTA = 1,    /* gated delta rule: short causal filter + SiLU on q/k/v, unit-length q/k, per-head decay
                           exp(-exp(A_log) softplus(a + dt_bias)), write strength sigmoid(b), read-out RMS-normed per head
                           and gated by SiLU(g) */
-  XB_MIX_PARALLEL = 2  /* two mixers on the same input, summed with left_scale / right_scale:
+  XB_MIX_PARALLEL = 2, /* two mixers on the same input, summed with left_scale / right_scale:
                           left = grouped-query softmax attention without rotation, causal window + kept first tokens,
                                  q/k/v bias, sigmoid output gate;
                           right = HGRN2 (forget gate f = lower + (1 - lower) sigmoid(.), input gate 1 - f), read-out
                                  RMS-normed per head */
+  XB_MIX_LATENT = 3,   /* softmax attention over a cached latent: keys and values are per-head up-projections of one
+                          RMS-normed vector of m_kv_rank numbers per token, plus one rotated key part of m_rot_dim numbers
+                          that all heads share (interleaved rotary pairs on its first m_rot_dims entries, base
+                          m_rot_base); causal; the cache holds the latent and the rotated part only */
+  XB_MIX_GDELTA = 4,   /* delta rule with a decay and a removal rate per head and key channel:
+                          S <- diag(w) S - (a*u)(u^T S) + k v^T, o = S^T r; w = exp(-e^-1/2 sigmoid(W2 tanh(W1 h) + w0))
+                          (W1 of m_rank rows), a = sigmoid(.), u = unit k; read-out RMS-normed per head, weighted, gated
+                          by sigmoid(g) */
+  XB_MIX_LIGHTNING = 5 /* linear attention with a constant decay per head: S <- decay S + k v^T, o = S^T q, SiLU on
+                          q, k, v; read-out RMS-normed over all heads together, weighted, gated by sigmoid(g) */
+};
+
+enum {
+  XB_FF_RELU2 = 0,     /* down(relu(up h)^2) */
+  XB_FF_GLU_CLAMP = 1, /* down(g sigmoid(1.702 g) (u + 1)), g = min(gate h, limit), u = clamp(up h, -limit, limit); biases */
+  XB_FF_MOE = 2        /* n_experts such feed-forwards without biases, each token uses `top` of them: sigmoid router scores,
+                          experts in `groups` equal groups of neighbours, a group scores the sum of its two best experts and
+                          only the `keep_groups` best groups stay eligible; weights = scores * route_scale; plus an
+                          always-on shared expert of width shared_ff (0 = none) */
 };
 
 typedef struct xb_hybrid_layer {
@@ -232,6 +251,17 @@ typedef struct xb_hybrid_layer {
   float a_scale;                                                      /* score = q.k * a_scale */
   int32_t r_heads, r_dim, r_vdim;                                     /* XB_MIX_PARALLEL, right */
   float left_scale, right_scale;
+  /* XB_MIX_LATENT / XB_MIX_GDELTA / XB_MIX_LIGHTNING: heads, per-head key size (unrotated part for LATENT), value size
+   * (GDELTA: = m_dim), and for LATENT the rotated part, the latent's size and how many entries of the rotated part turn */
+  int32_t m_heads, m_dim, m_vdim, m_rot_dim, m_kv_rank, m_rot_dims;
+  int32_t m_rank;                                   /* GDELTA: rows of the decay's first projection */
+  float m_scale, m_rot_base;                        /* LATENT: score scale, rotary base */
+  int32_t ff_kind;                                  /* XB_FF_* (ff = width of the dense feed-forward or of one expert) */
+  float ff_limit;
+  int32_t n_experts, top, groups, keep_groups, shared_ff;   /* XB_FF_MOE; groups 0 = no group limit */
+  float route_scale, shared_limit;
+  int32_t weights_of;                               /* >= 0: this layer owns no tensors and uses that layer's (with a cache
+                                                       and state of its own); -1: its own */
 } xb_hybrid_layer;
 
 typedef struct xb_hybrid_desc {
@@ -244,12 +274,22 @@ typedef struct xb_hybrid_desc {
   int32_t compute_fp32;              /* 0: Linears read bf16 activations (serving); 1: everything in fp32, plain FMA */
   int32_t max_batch_tokens, max_seqs;
   int32_t max_logit_rows;            /* most rows one xb_forward_rows call may ask logits for */
+  int32_t block;                     /* XB_BLOCK_*: how a layer's sublayers meet the residual stream */
+  int32_t norm_scalar;               /* 1: the stream's norms ("l<i>.norm1", "final.norm") carry one number, used as it is */
+  float embed_scale;                 /* the embedding row is multiplied by this (1 = as stored) */
 } xb_hybrid_desc;
+
+enum {
+  XB_BLOCK_SANDWICH = 0,  /* mixer, then feed-forward, each reading its own norm through a causal filter, each branch
+                             normed before it is added; optional token side input (the Refatar layout) */
+  XB_BLOCK_PARALLEL = 1   /* one norm per layer; mixer and feed-forward read it and their sum is added: x += mix(h) + ff(h) */
+};
 
 int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybrid_layer* layers, int device, xb_engine** out);
 
 /* One tensor of a hybrid model by its checkpoint name ("embed", "l3.mix.q.conv", "l1.mix.left.q.b", ...), from host
- * or device memory.  dtype: 0 bf16, 1 fp16, 2 fp32.  xb_load_safetensors feeds a hybrid engine through the same
+ * or device memory.  Per-head constants of a configuration travel the same way ("l<i>.mix.decay", fp32 [heads], for
+ * XB_MIX_LIGHTNING).  dtype: 0 bf16, 1 fp16, 2 fp32.  xb_load_safetensors feeds a hybrid engine through the same
  * name table; xb_weights_missing lists what is still absent. */
 int xb_load_named(xb_engine* e, const char* name, const void* src, int dtype, const int64_t* shape, int ndim);
 

@@ -37,7 +37,7 @@ class ModelDesc(C.Structure):
   ]
 
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 def model_desc(**fields) -> ModelDesc:
@@ -45,7 +45,9 @@ def model_desc(**fields) -> ModelDesc:
   return ModelDesc(struct_size=C.sizeof(ModelDesc), **fields)
 
 
-MIX_DELTA, MIX_PARALLEL = 1, 2
+MIX_DELTA, MIX_PARALLEL, MIX_LATENT, MIX_GDELTA, MIX_LIGHTNING = 1, 2, 3, 4, 5
+FF_RELU2, FF_GLU_CLAMP, FF_MOE = 0, 1, 2
+BLOCK_SANDWICH, BLOCK_PARALLEL = 0, 1
 ST_BF16, ST_F16, ST_F32 = 0, 1, 2   # element types xb_load_named accepts
 
 
@@ -58,6 +60,12 @@ class HybridLayer(C.Structure):
     ("a_window", C.c_int32), ("a_keep_first", C.c_int32), ("a_scale", C.c_float),
     ("r_heads", C.c_int32), ("r_dim", C.c_int32), ("r_vdim", C.c_int32),
     ("left_scale", C.c_float), ("right_scale", C.c_float),
+    ("m_heads", C.c_int32), ("m_dim", C.c_int32), ("m_vdim", C.c_int32), ("m_rot_dim", C.c_int32), ("m_kv_rank", C.c_int32),
+    ("m_rot_dims", C.c_int32), ("m_rank", C.c_int32), ("m_scale", C.c_float), ("m_rot_base", C.c_float),
+    ("ff_kind", C.c_int32), ("ff_limit", C.c_float),
+    ("n_experts", C.c_int32), ("top", C.c_int32), ("groups", C.c_int32), ("keep_groups", C.c_int32), ("shared_ff", C.c_int32),
+    ("route_scale", C.c_float), ("shared_limit", C.c_float),
+    ("weights_of", C.c_int32),
   ]
 
 
@@ -67,6 +75,7 @@ class HybridDesc(C.Structure):
     ("n_layers", C.c_int32), ("dim", C.c_int32), ("vocab", C.c_int32), ("taps", C.c_int32), ("side_dim", C.c_int32),
     ("norm_eps", C.c_float), ("logit_softcap", C.c_float), ("compute_fp32", C.c_int32),
     ("max_batch_tokens", C.c_int32), ("max_seqs", C.c_int32), ("max_logit_rows", C.c_int32),
+    ("block", C.c_int32), ("norm_scalar", C.c_int32), ("embed_scale", C.c_float),
   ]
 
 

@@ -1294,6 +1294,9 @@ extern "C" int xb_engine_create_hybrid(const xb_hybrid_desc* desc, const xb_hybr
   XB_CHECK(h.dim <= 12288, "dim %d: the row kernels keep a row in 48 KB of shared memory (<= 12288)", h.dim);
   XB_CHECK(h.taps >= 0 && h.taps <= HY_MAX_TAPS && h.side_dim >= 0, "bad taps %d (0..%d) / side_dim %d", h.taps, HY_MAX_TAPS, h.side_dim);
   XB_CHECK(h.max_batch_tokens > 0 && h.max_seqs > 0 && h.max_logit_rows >= 0, "max_batch_tokens / max_seqs must be > 0");
+  XB_CHECK(h.block == XB_BLOCK_SANDWICH || h.block == XB_BLOCK_PARALLEL, "unknown block layout %d", h.block);
+  XB_CHECK(h.block == XB_BLOCK_SANDWICH || (h.taps == 0 && h.side_dim == 0), "parallel blocks carry no causal filter or token side input");
+  XB_CHECK(h.block == XB_BLOCK_PARALLEL || h.norm_scalar == 0, "sandwich blocks carry a norm weight per channel");
   xb_engine* e = new xb_engine();
   // the fields of the Llama-shaped description that the shared bookkeeping reads
   e->d = xb_model_desc{};

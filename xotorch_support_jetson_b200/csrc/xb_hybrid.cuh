@@ -32,6 +32,12 @@ struct HyLayer {
   bool tc_attn = false;
   CUtensorMap tmK, tmV;
   size_t st_rec = 0, st_conv = 0, st_canon1 = 0, st_canon2 = 0;   // float offsets inside a slot's state
+  // latent attention / general delta rule / lightning and the gated feed-forwards
+  int off_dkv = 0, off_r = 0, off_w1 = 0;   // more columns of the fused input projection
+  int n_up = 0, n_dn = 0;                   // rows of the fused up projection, inputs of the down projection
+  bf16 *w_uk = nullptr, *w_uv = nullptr, *w_d2 = nullptr, *w_router = nullptr, *t_d2 = nullptr;
+  float *b_up = nullptr, *b_down = nullptr, *lat_norm = nullptr, *rot_freq = nullptr, *w0 = nullptr, *hdecay = nullptr;
+  int owner = -1;                           // layer whose tensors this one uses (weights_of), -1: its own
 };
 
 struct HyModel {
@@ -56,6 +62,9 @@ struct HyModel {
   bool finalized = false;
   // steps of few rows are chains of short kernels: their launches overlap (programmatic serialization); prompts run long
   // kernels, where blocks of the next kernel parked on the SMs cost more than the launch gap (measured: +17% per prompt)
+  float *qa = nullptr, *gw = nullptr;   // latent attention: queries in the cache's space [T, H * (rank + rot)]; experts: weights [T, E]
+  void* ah = nullptr;                  // parallel blocks: the normed stream as a Linear input (both sublayers read it)
+  size_t maxQA = 0, maxE = 0, maxM = 0;   // maxM: widest matrix that passes through the m1 / m2 buffers besides the stream's width
   bool pdl_now = false;
   int recur_lpc = 0;         // XB_HY_LPC=4|8|16 pins the lanes per state column (A/B); 0: by the step's shape
   int use_tc_attn = 1;       // XB_HY_TC_ATTN=0: attention through the per-token kernel everywhere (A/B)
@@ -94,11 +103,175 @@ static void hy_destroy(HyModel* hy) {
   for (void* p : hy->allocs) cudaFree(p);
   for (HyLayer& l : hy->L) {
     cudaFree(l.k_pool); cudaFree(l.v_pool);
+    if (l.owner >= 0) continue;   // the tile-major copies belong to the layer that owns the tensors
     cudaFree(l.t_in); cudaFree(l.t_o); cudaFree(l.t_o2); cudaFree(l.t_up); cudaFree(l.t_down); cudaFree(l.t_sgate); cudaFree(l.t_sproj);
+    cudaFree(l.t_d2);
   }
   cudaFree(hy->t_head);
   cudaFree(hy->state);
   delete hy;
+}
+
+// A matrix that occupies columns [col0, col0 + cols) of a fused bf16 matrix with `ld` columns (the down projections of
+// experts side by side are ONE matrix over all experts' activations).
+static void hy_name_cols(HyModel* hy, const std::string& name, bf16* base, long long col0, long long rows, long long cols, long long ld) {
+  hy_name(hy, name, base + col0, false, rows, cols, ld, 2);
+}
+
+// Mixers of the parallel-block designs.  own: the layer has tensors of its own (else only cache / state is laid out).
+static int hy_create_mixer(xb_engine* e, int i, bool own, size_t& st, uint64_t& wbytes, uint64_t& kvpos) {
+  HyModel* hy = e->hy;
+  HyLayer& l = hy->L[i];
+  const xb_hybrid_layer& c = l.d;
+  const xb_hybrid_desc& d = hy->d;
+  const size_t D = d.dim;
+  const std::string p = "l" + std::to_string(i) + ".mix.";
+  const long long H = c.m_heads, n = c.m_dim;
+  XB_CHECK(H > 0 && n > 0, "layer %d: bad mixer sizes", i);
+  if (c.mixer == XB_MIX_LATENT) {
+    const long long dr = c.m_rot_dim, dv = c.m_vdim, R = c.m_kv_rank;
+    XB_CHECK(dr >= 0 && dv > 0 && R > 0 && R <= 512, "layer %d: bad latent attention sizes (latent of at most 512 numbers)", i);
+    XB_CHECK(c.m_rot_dims >= 0 && c.m_rot_dims <= dr && c.m_rot_dims % 2 == 0, "layer %d: %d rotating entries do not fit a part of %lld", i,
+             c.m_rot_dims, dr);
+    l.off_q = 0; l.off_dkv = (int)(H * (n + dr));
+    l.n_in = l.off_dkv + (int)(R + dr);
+    l.n_o = (int)(H * dv);
+    if (own) {
+      XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+      XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
+      XB_TRY(hy_alloc_t(hy, &l.w_uk, (size_t)(H * n * R)));
+      XB_TRY(hy_alloc_t(hy, &l.w_uv, (size_t)(H * dv * R)));
+      XB_TRY(hy_alloc_t(hy, &l.lat_norm, (size_t)R));
+      hy_name_rows(hy, p + "q", l.w_in, l.off_q, H * (n + dr), D);
+      hy_name_rows(hy, p + "dkv", l.w_in, l.off_dkv, R + dr, D);
+      hy_name_vec(hy, p + "dkv.norm", l.lat_norm, R);
+      hy_name_rows(hy, p + "uk", l.w_uk, 0, H * n, R);
+      hy_name_rows(hy, p + "uv", l.w_uv, 0, H * dv, R);
+      hy_name_rows(hy, p + "o", l.w_o, 0, D, l.n_o);
+      const int half = c.m_rot_dims / 2;
+      std::vector<float> fr((size_t)(half > 0 ? half : 1), 0.f);
+      for (int j = 0; j < half; ++j) fr[j] = (float)pow((double)c.m_rot_base, -2.0 * j / (double)c.m_rot_dims);
+      XB_TRY(hy_alloc_t(hy, &l.rot_freq, fr.size()));
+      XB_CUDA(cudaMemcpy(l.rot_freq, fr.data(), fr.size() * sizeof(float), cudaMemcpyHostToDevice));
+      wbytes += ((size_t)l.n_in * D + D * l.n_o + (size_t)(H * (n + dv) * R)) * 2;
+    }
+    const size_t qa = (size_t)(H * (R + dr)), ol = (size_t)(H * R);
+    if (qa > hy->maxQA) hy->maxQA = qa;
+    if (ol > hy->maxO) hy->maxO = ol;
+    kvpos += (uint64_t)(R + dr) * (d.compute_fp32 ? 4 : 2);
+  } else if (c.mixer == XB_MIX_GDELTA) {
+    const long long HN = H * n, rk = c.m_rank;
+    XB_CHECK(n <= HY_MAX_KDIM && rk > 0, "layer %d: bad delta-rule sizes (key dim <= %d)", i, HY_MAX_KDIM);
+    l.off_r = 0; l.off_k = (int)HN; l.off_v = (int)(2 * HN); l.off_g = (int)(3 * HN); l.off_a = (int)(4 * HN); l.off_w1 = (int)(5 * HN);
+    l.n_in = l.off_w1 + (int)rk;
+    l.n_o = (int)HN;
+    if (own) {
+      XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+      XB_TRY(hy_alloc_t(hy, &l.b_in, (size_t)l.n_in));
+      XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
+      XB_TRY(hy_alloc_t(hy, &l.w_d2, (size_t)(HN * rk)));
+      XB_TRY(hy_alloc_t(hy, &l.w0, (size_t)HN));
+      XB_TRY(hy_alloc_t(hy, &l.head_norm, (size_t)HN));
+      hy_name_rows(hy, p + "r", l.w_in, l.off_r, HN, D);
+      hy_name_rows(hy, p + "k", l.w_in, l.off_k, HN, D);
+      hy_name_rows(hy, p + "v", l.w_in, l.off_v, HN, D);
+      hy_name_rows(hy, p + "g", l.w_in, l.off_g, HN, D);
+      hy_name_rows(hy, p + "a", l.w_in, l.off_a, HN, D);   hy_name_vec(hy, p + "a.b", l.b_in + l.off_a, HN);
+      hy_name_rows(hy, p + "w1", l.w_in, l.off_w1, rk, D);
+      hy_name_rows(hy, p + "w2", l.w_d2, 0, HN, rk);
+      hy_name_vec(hy, p + "w0", l.w0, HN);
+      hy_name_vec(hy, p + "norm", l.head_norm, HN);
+      hy_name_rows(hy, p + "o", l.w_o, 0, D, l.n_o);
+      wbytes += ((size_t)l.n_in * D + D * l.n_o + (size_t)(HN * rk)) * 2;
+    }
+    l.st_rec = st; st += (size_t)(HN * n);
+    if ((size_t)H > hy->maxH) hy->maxH = H;
+    if ((size_t)(6 * HN) > hy->maxC) hy->maxC = 6 * HN;
+    if ((size_t)l.n_o > hy->maxO) hy->maxO = l.n_o;
+    if ((size_t)rk > hy->maxK) hy->maxK = rk;
+    if ((size_t)HN > hy->maxM) hy->maxM = HN;
+  } else {
+    const long long dv = c.m_vdim;
+    XB_CHECK(n <= HY_MAX_KDIM && dv > 0, "layer %d: bad lightning sizes (key dim <= %d)", i, HY_MAX_KDIM);
+    l.off_q = 0; l.off_k = (int)(H * n); l.off_v = (int)(2 * H * n); l.off_g = l.off_v + (int)(H * dv);
+    l.n_in = l.off_g + (int)(H * dv);
+    l.n_o = (int)(H * dv);
+    if (own) {
+      XB_TRY(hy_alloc_t(hy, &l.w_in, (size_t)l.n_in * D));
+      XB_TRY(hy_alloc_t(hy, &l.w_o, D * l.n_o));
+      XB_TRY(hy_alloc_t(hy, &l.head_norm, (size_t)(H * dv)));
+      XB_TRY(hy_alloc_t(hy, &l.hdecay, (size_t)H));
+      hy_name_rows(hy, p + "q", l.w_in, l.off_q, H * n, D);
+      hy_name_rows(hy, p + "k", l.w_in, l.off_k, H * n, D);
+      hy_name_rows(hy, p + "v", l.w_in, l.off_v, H * dv, D);
+      hy_name_rows(hy, p + "g", l.w_in, l.off_g, H * dv, D);
+      hy_name_vec(hy, p + "norm", l.head_norm, H * dv);
+      hy_name_vec(hy, p + "decay", l.hdecay, H);       // from the configuration, not the checkpoint
+      hy_name_rows(hy, p + "o", l.w_o, 0, D, l.n_o);
+      wbytes += ((size_t)l.n_in * D + D * l.n_o) * 2;
+    }
+    l.st_rec = st; st += (size_t)(H * dv * n);
+    const size_t cc = (size_t)(2 * H * n + H * dv);
+    if (cc > hy->maxC) hy->maxC = cc;
+    if ((size_t)l.n_o > hy->maxO) hy->maxO = l.n_o;
+  }
+  return 0;
+}
+
+// Gated feed-forwards: dense (gate | up rows of one matrix, biases) or experts (every expert's gate | up rows, then the
+// shared expert's, in one matrix; every expert's down projection side by side as the columns of one matrix).
+static int hy_create_ff(xb_engine* e, int i, bool own, uint64_t& wbytes) {
+  HyModel* hy = e->hy;
+  HyLayer& l = hy->L[i];
+  const xb_hybrid_layer& c = l.d;
+  const size_t D = hy->d.dim, F = c.ff;
+  const std::string p = "l" + std::to_string(i) + ".mlp.";
+  XB_CHECK(hy->d.block == XB_BLOCK_PARALLEL, "layer %d: gated feed-forwards belong to parallel blocks", i);
+  if (c.ff_kind == XB_FF_GLU_CLAMP) {
+    l.n_up = (int)(2 * F); l.n_dn = (int)F;
+    if (own) {
+      XB_TRY(hy_alloc_t(hy, &l.w_up, (size_t)l.n_up * D));
+      XB_TRY(hy_alloc_t(hy, &l.b_up, (size_t)l.n_up));
+      XB_TRY(hy_alloc_t(hy, &l.w_down, D * F));
+      XB_TRY(hy_alloc_t(hy, &l.b_down, D));
+      hy_name_rows(hy, p + "gate", l.w_up, 0, F, D);   hy_name_vec(hy, p + "gate.b", l.b_up, F);
+      hy_name_rows(hy, p + "up", l.w_up, F, F, D);     hy_name_vec(hy, p + "up.b", l.b_up + F, F);
+      hy_name_rows(hy, p + "down", l.w_down, 0, D, F); hy_name_vec(hy, p + "down.b", l.b_down, D);
+    }
+  } else if (c.ff_kind == XB_FF_MOE) {
+    const size_t E = c.n_experts, S = c.shared_ff > 0 ? c.shared_ff : 0;
+    XB_CHECK(E > 0 && c.top > 0 && (size_t)c.top <= E, "layer %d: %d experts, %d per token", i, c.n_experts, c.top);
+    XB_CHECK(c.groups == 0 || (c.groups > 0 && E % c.groups == 0 && c.keep_groups > 0 && c.keep_groups <= c.groups &&
+                               (size_t)c.top <= (E / c.groups) * c.keep_groups),
+             "layer %d: %d groups (%d kept) do not fit %d experts with %d per token", i, c.groups, c.keep_groups, c.n_experts, c.top);
+    l.n_up = (int)(2 * (E * F + S)); l.n_dn = (int)(E * F + S);
+    if (own) {
+      XB_TRY(hy_alloc_t(hy, &l.w_up, (size_t)l.n_up * D));
+      XB_TRY(hy_alloc_t(hy, &l.w_down, D * l.n_dn));
+      XB_TRY(hy_alloc_t(hy, &l.w_router, E * D));
+      hy_name_rows(hy, p + "router", l.w_router, 0, E, D);
+      for (size_t x = 0; x < E; ++x) {
+        const std::string pe = p + "e" + std::to_string(x) + ".";
+        hy_name_rows(hy, pe + "gate", l.w_up, 2 * x * F, F, D);
+        hy_name_rows(hy, pe + "up", l.w_up, 2 * x * F + F, F, D);
+        hy_name_cols(hy, pe + "down", l.w_down, x * F, D, F, l.n_dn);
+      }
+      if (S > 0) {
+        hy_name_rows(hy, p + "shared.gate", l.w_up, 2 * E * F, S, D);
+        hy_name_rows(hy, p + "shared.up", l.w_up, 2 * E * F + S, S, D);
+        hy_name_cols(hy, p + "shared.down", l.w_down, E * F, D, S, l.n_dn);
+      }
+      wbytes += E * D * 2;
+    }
+    if (E > hy->maxE) hy->maxE = E;
+    if (E > hy->maxM) hy->maxM = E;
+  } else {
+    return xb_fail(1, "layer %d: unknown feed-forward kind %d", i, c.ff_kind);
+  }
+  if (own) wbytes += ((size_t)l.n_up * D + D * l.n_dn) * 2;
+  if ((size_t)l.n_up > hy->maxN) hy->maxN = l.n_up;
+  if ((size_t)l.n_dn > hy->maxK) hy->maxK = l.n_dn;
+  return 0;
 }
 
 static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_layer* layers) {
@@ -117,10 +290,26 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     l.d = layers[i];
     const xb_hybrid_layer& c = l.d;
     const std::string p = "l" + std::to_string(i) + ".";
-    XB_TRY(hy_alloc_t(hy, &l.norm1, D)); hy_name_vec(hy, p + "norm1", l.norm1, D);
-    XB_TRY(hy_alloc_t(hy, &l.norm1b, D)); hy_name_vec(hy, p + "norm1b", l.norm1b, D);
+    const bool own = c.weights_of < 0;
+    const bool sandwich = d.block == XB_BLOCK_SANDWICH;
+    l.owner = -1;
+    if (!own) {
+      XB_CHECK(c.weights_of < d.n_layers && c.weights_of != i && layers[c.weights_of].weights_of < 0,
+               "layer %d: weights_of %d must name another layer that owns its tensors", i, c.weights_of);
+      const xb_hybrid_layer& o = layers[c.weights_of];
+      XB_CHECK(o.mixer == c.mixer && o.ff == c.ff && o.ff_kind == c.ff_kind, "layer %d: its description differs from layer %d's, whose tensors it uses",
+               i, c.weights_of);
+      l.owner = c.weights_of;
+    }
+    XB_CHECK(own || (c.mixer != XB_MIX_DELTA && c.mixer != XB_MIX_PARALLEL), "layer %d: this mixer kind keeps tensors of its own", i);
+    const size_t nd = d.norm_scalar ? 1 : D;   // numbers in a norm of the stream
+    if (own) {
+      XB_TRY(hy_alloc_t(hy, &l.norm1, nd));
+      hy_name_vec(hy, p + "norm1", l.norm1, nd);
+      if (sandwich) { XB_TRY(hy_alloc_t(hy, &l.norm1b, D)); hy_name_vec(hy, p + "norm1b", l.norm1b, D); }
+    }
     if (ct > 0) {
-      XB_TRY(hy_alloc_t(hy, &l.canon1, D * ct)); hy_name(hy, p + "canon1", l.canon1, true, D, ct, ct, 2);
+      if (own) { XB_TRY(hy_alloc_t(hy, &l.canon1, D * ct)); hy_name(hy, p + "canon1", l.canon1, true, D, ct, ct, 2); }
       l.st_canon1 = st; st += (size_t)(ct - 1) * D;
     }
     if (c.mixer == XB_MIX_DELTA) {
@@ -194,13 +383,18 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
       if ((size_t)l.n_o2 > hy->maxO) hy->maxO = l.n_o2;
       wbytes += ((size_t)l.n_in * D + D * l.n_o + D * l.n_o2) * 2;
       kvpos += (uint64_t)G * (dk + dv) * (d.compute_fp32 ? 4 : 2);
+    } else if (c.mixer == XB_MIX_LATENT || c.mixer == XB_MIX_GDELTA || c.mixer == XB_MIX_LIGHTNING) {
+      XB_TRY(hy_create_mixer(e, i, own, st, wbytes, kvpos));
     } else {
       return xb_fail(1, "layer %d: unknown mixer kind %d", i, c.mixer);
     }
     if ((size_t)l.n_in > hy->maxN) hy->maxN = l.n_in;
     if ((size_t)l.n_o > hy->maxK) hy->maxK = l.n_o;
     if ((size_t)l.n_o2 > hy->maxK) hy->maxK = l.n_o2;
-    if (c.ff > 0) {
+    if (c.ff > 0 && c.ff_kind != XB_FF_RELU2) {
+      XB_TRY(hy_create_ff(e, i, own, wbytes));
+    } else if (c.ff > 0) {
+      XB_CHECK(own && sandwich, "layer %d: the squared-ReLU feed-forward belongs to sandwich blocks with tensors of their own", i);
       const size_t F = c.ff;
       XB_TRY(hy_alloc_t(hy, &l.norm2, D)); hy_name_vec(hy, p + "norm2", l.norm2, D);
       XB_TRY(hy_alloc_t(hy, &l.norm2b, D)); hy_name_vec(hy, p + "norm2b", l.norm2b, D);
@@ -223,9 +417,18 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
     }
   }
   hy->state_floats = st;
+  // layers that use another layer's tensors: the same device pointers, a cache and state of their own
+  for (int i = 0; i < d.n_layers; ++i) {
+    HyLayer& l = hy->L[i];
+    if (l.owner < 0) continue;
+    const HyLayer& o = hy->L[l.owner];
+    l.w_in = o.w_in; l.b_in = o.b_in; l.w_o = o.w_o; l.w_up = o.w_up; l.w_down = o.w_down; l.norm1 = o.norm1; l.head_norm = o.head_norm;
+    l.w_uk = o.w_uk; l.w_uv = o.w_uv; l.w_d2 = o.w_d2; l.w_router = o.w_router; l.b_up = o.b_up; l.b_down = o.b_down;
+    l.lat_norm = o.lat_norm; l.rot_freq = o.rot_freq; l.w0 = o.w0; l.hdecay = o.hdecay; l.canon1 = o.canon1;
+  }
   XB_TRY(hy_alloc_t(hy, &hy->embed, (size_t)d.vocab * D)); hy_name_rows(hy, "embed", hy->embed, 0, d.vocab, D);
   XB_TRY(hy_alloc_t(hy, &hy->head, (size_t)d.vocab * D)); hy_name_rows(hy, "head", hy->head, 0, d.vocab, D);
-  XB_TRY(hy_alloc_t(hy, &hy->final_norm, D)); hy_name_vec(hy, "final.norm", hy->final_norm, D);
+  XB_TRY(hy_alloc_t(hy, &hy->final_norm, d.norm_scalar ? 1 : D)); hy_name_vec(hy, "final.norm", hy->final_norm, d.norm_scalar ? 1 : D);
   if (d.side_dim > 0) {
     const size_t w = (size_t)d.side_dim * d.n_layers;
     XB_TRY(hy_alloc_t(hy, &hy->side_embed, (size_t)d.vocab * w)); hy_name_rows(hy, "side.embed", hy->side_embed, 0, d.vocab, w);
@@ -237,7 +440,8 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   XB_TRY(hy_alloc_t(hy, &hy->hn, Tm * D));
   const size_t ws_min = d.compute_fp32 ? 0 : ((size_t)32 << 20);   // room for the split-K planes of decode-sized batches
   hy->cap_P = Tm * hy->maxN * 4 > ws_min ? Tm * hy->maxN * 4 : ws_min;
-  hy->cap_m = Tm * D * 4 > ws_min ? Tm * D * 4 : ws_min;
+  const size_t wm = hy->maxM > D ? hy->maxM : D;
+  hy->cap_m = Tm * wm * 4 > ws_min ? Tm * wm * 4 : ws_min;
   XB_TRY(hy_alloc(hy, (void**)&hy->P, hy->cap_P));
   XB_TRY(hy_alloc_t(hy, &hy->c, Tm * hy->maxC));
   XB_TRY(hy_alloc_t(hy, &hy->o, Tm * hy->maxO));
@@ -249,6 +453,9 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   XB_TRY(hy_alloc(hy, &hy->a1, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->a2, Tm * hy->maxK * as));
   XB_TRY(hy_alloc(hy, &hy->head_in, R * D * as));
+  if (d.block == XB_BLOCK_PARALLEL) XB_TRY(hy_alloc(hy, &hy->ah, Tm * D * as));
+  if (hy->maxQA > 0) XB_TRY(hy_alloc_t(hy, &hy->qa, Tm * hy->maxQA));
+  if (hy->maxE > 0) XB_TRY(hy_alloc_t(hy, &hy->gw, Tm * hy->maxE));
   hy->cap_head = R * (size_t)d.vocab * 4 > ws_min ? R * (size_t)d.vocab * 4 : ws_min;
   XB_TRY(hy_alloc(hy, (void**)&hy->head_raw, hy->cap_head));
   {
@@ -281,7 +488,7 @@ static int hy_store(xb_engine* e, const std::string& name, const void* src, int 
   XB_CHECK(dt >= 0 && dt <= 2, "tensor %s: unsupported element type", name.c_str());
   long long numel = 1;
   for (int i = 0; i < ndim; ++i) numel *= shape[i];
-  bool ok = numel == t.rows * t.cols && ndim == t.ndim;
+  bool ok = numel == t.rows * t.cols && (ndim == t.ndim || numel == 1);   // a single number may come without a shape
   if (ok && ndim == 2) ok = shape[0] == t.rows && shape[1] == t.cols;
   if (!ok) {
     std::string got;
@@ -326,13 +533,21 @@ static int hy_finalize(xb_engine* e) {
     return src != nullptr ? hy_tile(dst, src, rows, K) : 0;
   };
   for (HyLayer& l : hy->L) {
+    if (l.owner >= 0) continue;
+    const size_t n_up = l.n_up > 0 ? l.n_up : l.d.ff, n_dn = l.n_dn > 0 ? l.n_dn : l.d.ff;
     XB_TRY(retile(&l.t_in, l.w_in, l.n_in, D));
     XB_TRY(retile(&l.t_o, l.w_o, D, l.n_o));
     XB_TRY(retile(&l.t_o2, l.w_o2, D, l.n_o2));
-    XB_TRY(retile(&l.t_up, l.w_up, l.d.ff, D));
-    XB_TRY(retile(&l.t_down, l.w_down, D, l.d.ff));
+    XB_TRY(retile(&l.t_up, l.w_up, n_up, D));
+    XB_TRY(retile(&l.t_down, l.w_down, D, n_dn));
     XB_TRY(retile(&l.t_sgate, l.w_sgate, hy->d.side_dim, D));
     XB_TRY(retile(&l.t_sproj, l.w_sproj, D, hy->d.side_dim));
+    XB_TRY(retile(&l.t_d2, l.w_d2, (size_t)l.d.m_heads * l.d.m_dim, l.d.m_rank));
+  }
+  for (HyLayer& l : hy->L) {
+    if (l.owner < 0) continue;
+    const HyLayer& o = hy->L[l.owner];
+    l.t_in = o.t_in; l.t_o = o.t_o; l.t_up = o.t_up; l.t_down = o.t_down; l.t_d2 = o.t_d2;
   }
   XB_TRY(retile(&hy->t_head, hy->head, hy->d.vocab, D));
   return 0;
@@ -382,6 +597,12 @@ static int hy_reserve(xb_engine* e) {
   for (HyLayer& l : hy->L) {
     cudaFree(l.k_pool); cudaFree(l.v_pool);
     l.k_pool = l.v_pool = nullptr;
+    if (l.d.mixer == XB_MIX_LATENT) {   // one pool: a row holds the latent (key and value at once) and the rotated key part
+      const size_t kb = (size_t)e->n_pages * e->page_tokens * (l.d.m_kv_rank + l.d.m_rot_dim) * es;
+      XB_TRY(dmalloc(&l.k_pool, kb));
+      XB_CUDA(cudaMemset(l.k_pool, 0, kb));
+      continue;
+    }
     if (l.d.mixer != XB_MIX_PARALLEL) continue;
     const size_t kb = (size_t)e->n_pages * l.d.a_kv_heads * e->page_tokens * l.d.a_dim * es;
     const size_t vb = (size_t)e->n_pages * l.d.a_kv_heads * e->page_tokens * l.d.a_vdim * es;
@@ -492,16 +713,16 @@ static int hy_linear(xb_engine* e, const void* x, long long ldx, const bf16* w, 
 
 // one recurrence launch.  Lanes per state column: the fewest of 4, 8, 16 that still give two blocks per SM (one long
 // prompt wants many short chains, a batch of sequences few shuffles); then the fewest chunks per lane that cover the key dim.
-template <int LPC, bool DELTA>
+template <int LPC, int MODE>
 static int hy_recur_l(xb_engine* e, const RecurIn& in, float* state, long long ss, float* o, long long ldo, const BatchMeta& m,
                       int n_seqs, int H, int dk, int dv, cudaStream_t st) {
   constexpr int COLS = 128 / LPC;
   const dim3 grid(n_seqs, H, (dv + COLS - 1) / COLS);
 #define HY_RECUR_CASE(NCH)                                                                                               \
   if (dk <= 4 * LPC * NCH) {                                                                                             \
-    const size_t smem = (size_t)2 * HY_TS * (8 * LPC * NCH + COLS + 4) * sizeof(float);                                  \
-    if (smem > 48 * 1024) XB_SMEM_ATTR_ONCE((hy_recur_kernel<NCH, LPC, DELTA>), smem);                                   \
-    return hy_launch(e, hy_recur_kernel<NCH, LPC, DELTA>, grid, dim3(128), smem, st, in, state, ss, o, ldo, m, H, dk, dv); \
+    const size_t smem = (size_t)2 * HY_TS * (hy_rec_vectors(MODE) * 4 * LPC * NCH + COLS + 4) * sizeof(float);           \
+    if (smem > 48 * 1024) XB_SMEM_ATTR_ONCE((hy_recur_kernel<NCH, LPC, MODE>), smem);                                    \
+    return hy_launch(e, hy_recur_kernel<NCH, LPC, MODE>, grid, dim3(128), smem, st, in, state, ss, o, ldo, m, H, dk, dv); \
   }
   HY_RECUR_CASE(1)
   HY_RECUR_CASE(2)
@@ -511,7 +732,7 @@ static int hy_recur_l(xb_engine* e, const RecurIn& in, float* state, long long s
 #undef HY_RECUR_CASE
   return xb_fail(1, "recurrent key dim %d exceeds %d", dk, HY_MAX_KDIM);
 }
-template <bool DELTA>
+template <int MODE>
 static int hy_recur(xb_engine* e, const RecurIn& in, float* state, long long ss, float* o, long long ldo, const BatchMeta& m, int n_seqs,
                     int H, int dk, int dv, cudaStream_t st) {
   int lpc = e->hy->recur_lpc;
@@ -521,9 +742,9 @@ static int hy_recur(xb_engine* e, const RecurIn& in, float* state, long long ss,
     if ((long long)n_seqs * H * ((dv + 31) / 32) >= want) lpc = 4;
     else if ((long long)n_seqs * H * ((dv + 15) / 16) >= want) lpc = 8;
   }
-  if (lpc == 4) return hy_recur_l<4, DELTA>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
-  if (lpc == 8) return hy_recur_l<8, DELTA>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
-  return hy_recur_l<16, DELTA>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
+  if (lpc == 4) return hy_recur_l<4, MODE>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
+  if (lpc == 8) return hy_recur_l<8, MODE>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
+  return hy_recur_l<16, MODE>(e, in, state, ss, o, ldo, m, n_seqs, H, dk, dv, st);
 }
 
 // causal per-channel filter over T rows (+ the slots' new tails): tap counts up to 4 through the tiled kernel, which in a
@@ -593,12 +814,20 @@ static int hy_attn_tc(xb_engine* e, const HyLayer& l, const BatchMeta& m, const 
 }
 
 template <typename AT>
+static int hy_row_op_launch(xb_engine* e, int T, const RowOpArgs& a, cudaStream_t st);
+template <typename AT>
 static int hy_row_op(xb_engine* e, int T, LinOut m1, float s1, LinOut m2, float s2, const float* bw, float bw_one, const float* nw,
                      void* xa, cudaStream_t st) {
   HyModel* hy = e->hy;
   RowOpArgs a;
   a.x = hy->x; a.m1 = m1; a.m2 = m2; a.s1 = s1; a.s2 = s2; a.bw = bw; a.bw_one = bw_one; a.nw = nw; a.hn = hy->hn; a.xa = xa;
   a.eps = hy->d.norm_eps; a.D = hy->d.dim;
+  a.m3 = hy_none(); a.ha = nullptr; a.plain_add = 0; a.nw_mode = 0;
+  return hy_row_op_launch<AT>(e, T, a, st);
+}
+template <typename AT>
+static int hy_row_op_launch(xb_engine* e, int T, const RowOpArgs& a, cudaStream_t st) {
+  HyModel* hy = e->hy;
   if (T <= 64 && hy->d.dim >= 1024)   // decode-sized batches: few rows, so more threads per row keep more loads in flight
     return hy_launch(e, hy_row_op_kernel<AT, 1024>, dim3(T), dim3(1024), (size_t)hy->d.dim * sizeof(float), st, a);
   return hy_launch(e, hy_row_op_kernel<AT, 256>, dim3(T), dim3(256), (size_t)hy->d.dim * sizeof(float), st, a);
@@ -613,10 +842,138 @@ static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, bool no_span, cons
                        reinterpret_cast<AT*>(hy->a1), (long long)D, st);
 }
 
+// ----------------------------------------------------------------------------- parallel blocks
+// x <- embed * scale;  per layer: h = norm(x) (made by the previous row op), x += mixer(h) + ff(h).
+// The mixers: latent attention (cache = latent + rotated key part, queries folded into the latent space so that a step
+// never rebuilds keys or values of earlier tokens), general delta rule, lightning; feed-forwards: clamped GLU, dense or experts.
+template <typename AT>
+static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, cudaStream_t st, LinOut* y) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_layer& c = l.d;
+  const int D = hy->d.dim;
+  AT* a2 = reinterpret_cast<AT*>(hy->a2);
+  LinOut U;
+  XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_up, l.t_up, l.b_up, T, l.n_up, D, hy->P, hy->cap_P, st, &U));
+  if (c.ff_kind == XB_FF_GLU_CLAMP) {
+    const long long n = (long long)T * c.ff;
+    XB_TRY(hy_launch(e, hy_glu_clamp_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, c.ff, c.ff_limit, a2, (long long)l.n_dn, T));
+  } else {
+    // router in fp32 whatever the serving type: the plain kernels accumulate and store fp32
+    LinOut z;
+    XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_router, nullptr, nullptr, T, c.n_experts, D, hy->m2, hy->cap_m, st, &z));
+    const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
+    XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, z, c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale,
+                     hy->gw, T));
+    const long long n = (long long)T * l.n_dn;
+    XB_TRY(hy_launch(e, hy_moe_act_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, (const float*)hy->gw, c.n_experts, c.ff,
+                     c.ff_limit, c.shared_ff > 0 ? c.shared_ff : 0, c.shared_limit, a2, (long long)l.n_dn, T));
+  }
+  return hy_linear<AT>(e, a2, l.n_dn, l.w_down, l.t_down, l.b_down, T, D, l.n_dn, hy->m2, hy->cap_m, st, y);
+}
+
+template <typename AT>
+static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps, cudaStream_t st, int with_head) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_desc& d = hy->d;
+  typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
+  BatchMeta m;
+  fill_batch_meta(e, m);
+  m.page_table = e->d_page_table;
+  m.tile_start = e->d_tile_start;
+  m.tile_len = e->d_tile_len;
+  m.max_pages = e->max_pages;
+  m.page_tokens = e->page_tokens;
+  const int D = d.dim;
+  const long long SS = (long long)hy->state_floats;
+  const int nwm = d.norm_scalar ? 2 : 1;
+  hy->pdl_now = T <= 128;
+  AT* a1 = reinterpret_cast<AT*>(hy->a1);
+  AT* a2 = reinterpret_cast<AT*>(hy->a2);
+  auto row_op = [&](LinOut y1, LinOut y2, const float* nw) -> int {
+    RowOpArgs a;
+    a.x = hy->x; a.m1 = y1; a.m2 = y2; a.m3 = hy_none(); a.s1 = 1.f; a.s2 = 1.f; a.bw = nullptr; a.bw_one = 0.f; a.nw = nw; a.hn = hy->hn;
+    a.xa = nullptr; a.ha = hy->ah; a.eps = d.norm_eps; a.D = D; a.plain_add = 1; a.nw_mode = nwm;
+    return hy_row_op_launch<AT>(e, T, a, st);
+  };
+  XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab,
+                   d.embed_scale));
+  XB_TRY(row_op(hy_none(), hy_none(), hy->L[0].norm1));
+  for (int li = 0; li < d.n_layers; ++li) {
+    const HyLayer& l = hy->L[li];
+    const xb_hybrid_layer& c = l.d;
+    const float* next_norm = li + 1 < d.n_layers ? hy->L[li + 1].norm1 : hy->final_norm;
+    LinOut P, y1, y2 = hy_none();
+    XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_in, l.t_in, l.b_in, T, l.n_in, D, hy->P, hy->cap_P, st, &P));
+    const int H = c.m_heads, n = c.m_dim;
+    if (c.mixer == XB_MIX_LATENT) {
+      const int dr = c.m_rot_dim, dv = c.m_vdim, R = c.m_kv_rank, W = R + dr;
+      XB_TRY(hy_launch(e, hy_latent_prep_kernel<KT>, dim3(T), dim3(256), 0, st, P, l.off_q, l.off_dkv, H, n, dr, R, c.m_rot_dims,
+                       (const float*)l.rot_freq, (const float*)l.lat_norm, d.norm_eps, (KT*)l.k_pool, m, hy->qa));
+      const size_t mm1 = (size_t)HY_MM_ROWS * n * sizeof(float), mm2 = (size_t)HY_MM_ROWS * R * sizeof(float);
+      XB_TRY(hy_launch(e, hy_head_mm_t_kernel, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm1, st, P, l.off_q, n + dr,
+                       (const bf16*)l.w_uk, hy->qa, (long long)H * W, W, T, n, R));
+      const int aw = 16;   // causal: every earlier key is visible
+      const size_t asm_bytes = (size_t)(((W + 3) & ~3) + aw * (2 + R)) * sizeof(float);
+      const LinOut Q = hy_plain(hy->qa, (long long)H * W);
+      const int far = 1 << 30;
+      if (R <= 256)
+        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
+                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R));
+      else
+        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
+                         (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R));
+      XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm2, st, (const float*)hy->o,
+                       (long long)H * R, (const bf16*)l.w_uv, a1, (long long)l.n_o, T, R, dv));
+    } else if (c.mixer == XB_MIX_GDELTA) {
+      const int HN = H * n, rk = c.m_rank;
+      LinOut Wd;
+      XB_TRY(hy_launch(e, hy_act_cols_kernel<AT>, dim3(T, (rk + 255) / 256), dim3(256), 0, st, P, l.off_w1, rk, 1, a2, (long long)rk));
+      XB_TRY(hy_linear<AT>(e, a2, rk, l.w_d2, l.t_d2, nullptr, T, HN, rk, hy->m2, hy->cap_m, st, &Wd));
+      XB_TRY(hy_launch(e, hy_gdelta_prep_kernel, dim3(T), dim3(256), 0, st, P, l.off_r, l.off_k, l.off_v, l.off_a, Wd, (const float*)l.w0,
+                       hy->c, (long long)6 * HN, hy->beta, hy->decay, H, n));
+      RecurIn in;
+      in.c = hy->c; in.ldc = 6LL * HN; in.qoff = 0; in.koff = HN; in.xoff[0] = 2LL * HN; in.xoff[1] = 3LL * HN; in.xoff[2] = 4LL * HN;
+      in.voff = 5LL * HN; in.q_heads = H; in.beta = hy->beta; in.decay = hy->decay; in.qk = nullptr; in.hdecay = nullptr;
+      XB_TRY(hy_recur<HY_REC_GDELTA>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, n_seqs, H, n, n, st));
+      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (H + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
+                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, n, n, 1));
+    } else {
+      const int dv = c.m_vdim;
+      const int nc = 2 * H * n + H * dv;
+      XB_TRY(hy_launch(e, hy_act_cols_kernel<float>, dim3(T, (nc + 255) / 256), dim3(256), 0, st, P, l.off_q, nc, 0, hy->c, (long long)nc));
+      RecurIn in;
+      in.c = hy->c; in.ldc = nc; in.qoff = 0; in.koff = (long long)H * n; in.voff = 2LL * H * n; in.q_heads = H;
+      in.xoff[0] = in.xoff[1] = in.xoff[2] = 0;
+      in.beta = in.decay = in.qk = nullptr; in.hdecay = l.hdecay;
+      XB_TRY(hy_recur<HY_REC_LIGHTNING>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, n_seqs, H, n, dv, st));
+      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, 1), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
+                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, 1, H * dv, 0, 1));
+    }
+    XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
+    if (c.ff > 0) XB_TRY(hy_ff_parallel<AT>(e, l, T, st, &y2));
+    XB_TRY(row_op(y1, y2, next_norm));
+    if (taps != nullptr && taps[li] != nullptr)
+      XB_CUDA(cudaMemcpyAsync(taps[li], hy->x, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  }
+  if (with_head) {
+    const int nr = e->sel_rows != nullptr ? e->sel_n : n_seqs;
+    if (nr > 0) {
+      const int* idx = e->sel_rows != nullptr ? hy->d_rows : m.seq_last;
+      LinOut y;
+      XB_TRY(hy_launch(e, hy_gather_rows_kernel<AT>, dim3(nr), dim3(256), 0, st, (const float*)hy->hn, idx, reinterpret_cast<AT*>(hy->head_in), D));
+      XB_TRY(hy_linear<AT>(e, hy->head_in, D, hy->head, hy->t_head, nullptr, nr, d.vocab, D, hy->head_raw, hy->cap_head, st, &y));
+      const long long tot = (long long)nr * d.vocab;
+      XB_TRY(hy_launch(e, hy_logits_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, st, y, d.logit_softcap, e->logits, nr, d.vocab));
+    }
+  }
+  return 0;
+}
+
 template <typename AT>
 static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* const* taps, cudaStream_t st, int with_head) {
   HyModel* hy = e->hy;
   const xb_hybrid_desc& d = hy->d;
+  if (d.block == XB_BLOCK_PARALLEL) return hy_run_parallel_t<AT>(e, T, n_seqs, taps, st, with_head);
   typedef typename std::conditional<std::is_same<AT, float>::value, float, bf16>::type KT;
   BatchMeta m;
   fill_batch_meta(e, m);
@@ -633,7 +990,8 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
   const bool side_fused = T <= 64 && (size_t)(2 * D + d.side_dim + 8) * sizeof(float) <= 48 * 1024;
   AT* a1 = reinterpret_cast<AT*>(hy->a1);
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
-  XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab));
+  XB_TRY(hy_launch(e, hy_embed_kernel, dim3(T), dim3(128), 0, st, (const int*)e->in_tokens, (const bf16*)hy->embed, hy->x, D, d.vocab,
+                   d.embed_scale));
   XB_TRY(hy_row_op<AT>(e, T, hy_none(), 0.f, hy_none(), 0.f, nullptr, 0.f, hy->L[0].norm1, nullptr, st));
   for (int li = 0; li < d.n_layers; ++li) {
     const HyLayer& l = hy->L[li];
@@ -653,11 +1011,12 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       {
         RecurIn in;
         in.c = hy->c; in.ldc = l.c_conv; in.qoff = 0; in.koff = (long long)G * dk; in.voff = 2LL * G * dk; in.q_heads = G;
-        in.beta = hy->beta; in.decay = hy->decay; in.qk = hy->qk;
-        XB_TRY(hy_recur<true>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, n_seqs, H, dk, dv, st));
+        in.beta = hy->beta; in.decay = hy->decay; in.qk = hy->qk; in.hdecay = nullptr;
+        in.xoff[0] = in.xoff[1] = in.xoff[2] = 0;
+        XB_TRY(hy_recur<HY_REC_DELTA>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, n_seqs, H, dk, dv, st));
       }
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (H + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
-                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv));
+                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, H, dv, 0, 0));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     } else {
       const int H = c.a_heads, G = c.a_kv_heads, dk = c.a_dim, dv = c.a_vdim;
@@ -689,8 +1048,8 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
         int aw = (c.a_window + c.a_keep_first + 63) / 64;
         aw = aw < 1 ? 1 : (aw > 16 ? 16 : aw);
         const size_t asm_bytes = (size_t)(((dk + 3) & ~3) + aw * (2 + dv)) * sizeof(float);
-        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT>, dim3(T, H), dim3(32 * aw), asm_bytes, st, P, l.off_q, l.off_g,
-                         (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f, a1,
+        XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, AT, 8>, dim3(T, H), dim3(32 * aw), asm_bytes, st, P, l.off_q, l.off_g,
+                         (const KT*)l.k_pool, (const KT*)l.v_pool, m, H, G, dk, dv, dk, dv, c.a_window, c.a_keep_first, c.a_scale, 1.0f, a1,
                          (long long)l.n_o));
       }
       const long long ldc = 2LL * Hr * rk + (long long)Hr * rv;
@@ -699,11 +1058,12 @@ static int hy_run_body_t(xb_engine* e, int T, int n_seqs, int n_tiles, void* con
       {
         RecurIn in;
         in.c = hy->c; in.ldc = ldc; in.qoff = 0; in.koff = (long long)Hr * rk; in.voff = 2LL * Hr * rk; in.q_heads = Hr;
-        in.beta = in.decay = in.qk = nullptr;
-        XB_TRY(hy_recur<false>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, n_seqs, Hr, rk, rv, st));
+        in.beta = in.decay = in.qk = in.hdecay = nullptr;
+        in.xoff[0] = in.xoff[1] = in.xoff[2] = 0;
+        XB_TRY(hy_recur<HY_REC_HGRN>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o2, m, n_seqs, Hr, rk, rv, st));
       }
       XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, (Hr + 7) / 8), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o2,
-                       (const float*)l.head_norm, P, -1, d.norm_eps, 1.0f, a2, (long long)l.n_o2, Hr, rv));
+                       (const float*)l.head_norm, P, -1, d.norm_eps, 1.0f, a2, (long long)l.n_o2, Hr, rv, 0, 0));
       XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
       XB_TRY(hy_linear<AT>(e, a2, l.n_o2, l.w_o2, l.t_o2, nullptr, T, D, l.n_o2, hy->m2, hy->cap_m, st, &y2));
       s1 = c.left_scale;

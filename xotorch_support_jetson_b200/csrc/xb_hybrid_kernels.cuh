@@ -19,6 +19,11 @@
 // data only after the wait (the whole chain of earlier kernels has then completed).
 #define HY_MAX_TAPS 16   // causal filters keep taps - 1 inputs per sequence
 #define HY_MAX_KDIM 256  // recurrent state: four lanes own one value column, up to 64 rows each
+// what one step does to a state column S_j (see hy_recur_kernel)
+#define HY_REC_HGRN 0
+#define HY_REC_DELTA 1
+#define HY_REC_GDELTA 2
+#define HY_REC_LIGHTNING 3
 
 struct LinOut {
   const float* f;      // fp32 [planes][T][ld] (planes summed per column, see SplitInfo), or nullptr
@@ -74,13 +79,13 @@ __device__ __forceinline__ SeqSpan seq_span(const BatchMeta& m, int s) {
 }
 
 // ----------------------------------------------------------------------------- embedding
-__global__ void hy_embed_kernel(const int* __restrict__ tokens, const bf16* __restrict__ emb, float* __restrict__ x, int D, int V) {
+__global__ void hy_embed_kernel(const int* __restrict__ tokens, const bf16* __restrict__ emb, float* __restrict__ x, int D, int V, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
-  for (int i = threadIdx.x; i < D; i += blockDim.x) x[(long long)t * D + i] = bf2f(emb[(long long)tok * D + i]);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) x[(long long)t * D + i] = bf2f(emb[(long long)tok * D + i]) * scale;
 }
 
 // ----------------------------------------------------------------------------- residual + norms, one block per row
@@ -88,18 +93,26 @@ __global__ void hy_embed_kernel(const int* __restrict__ tokens, const bf16* __re
 // x  += m / rms(m) * (bw + bw_one)                (bw_one = 1: weight stored as an offset from one; 0: plain weight)
 // hn  = x / rms(x) * (1 + nw)                     (the next reader's norm; skipped when nw == nullptr)
 // xa  = x as a Linear input                       (skipped when xa == nullptr)
+// plain_add: the branches are added as they are, x += s1 * m1 + s2 * m2 + m3 (no branch norm, bw unused).
+// nw_mode: 0 = weight stored as an offset from one (1 + nw[i]); 1 = plain weight nw[i]; 2 = one number nw[0].
+// ha  = hn as a Linear input                      (skipped when ha == nullptr)
 struct RowOpArgs {
   float* x;
-  LinOut m1, m2;
+  LinOut m1, m2, m3;
   float s1, s2;
   const float* bw;
   float bw_one;
   const float* nw;
   float* hn;
   void* xa;
+  void* ha;
   float eps;
   int D;
+  int plain_add, nw_mode;
 };
+__device__ __forceinline__ float hy_norm_weight(const float* nw, int mode, int i) {
+  return mode == 0 ? 1.0f + nw[i] : (mode == 1 ? nw[i] : nw[0]);
+}
 
 template <typename AT, int NT>
 __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
@@ -112,7 +125,29 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
   float* x = a.x + t * D;
   const bool branch = a.m1.f != nullptr || a.m1.h != nullptr;
   const bool two = a.m2.f != nullptr || a.m2.h != nullptr;
-  if (branch) {
+  if (branch && a.plain_add) {
+    const bool three = a.m3.f != nullptr || a.m3.h != nullptr;
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < D; i += NT) {
+      float b = a.s1 * lin_at(a.m1, t, i);
+      if (two) b += a.s2 * lin_at(a.m2, t, i);
+      if (three) b += lin_at(a.m3, t, i);
+      const float v = x[i] + b;
+      x[i] = v;
+      row[i] = v;
+      s2 += v * v;
+    }
+    if (a.nw == nullptr && a.xa == nullptr) return;
+    s2 = block_sum<NT>(s2, red);
+    if (a.nw != nullptr) {
+      const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
+      for (int i = threadIdx.x; i < D; i += NT) {
+        const float v = row[i] * inv2 * hy_norm_weight(a.nw, a.nw_mode, i);
+        a.hn[t * D + i] = v;
+        if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
+      }
+    }
+  } else if (branch) {
     float ss = 0.f;
     for (int i = threadIdx.x; i < D; i += NT) {
       float v = a.s1 * lin_at(a.m1, t, i);
@@ -145,7 +180,15 @@ __global__ void __launch_bounds__(NT) hy_row_op_kernel(RowOpArgs a) {
     s2 = block_sum<NT>(s2, red);
     if (a.nw != nullptr) {
       const float inv2 = 1.0f / sqrtf(s2 / (float)D + a.eps);
-      for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * (1.0f + a.nw[i]);
+      if (a.nw_mode == 0 && a.ha == nullptr) {
+        for (int i = threadIdx.x; i < D; i += NT) a.hn[t * D + i] = row[i] * inv2 * (1.0f + a.nw[i]);
+      } else {
+        for (int i = threadIdx.x; i < D; i += NT) {
+          const float v = row[i] * inv2 * hy_norm_weight(a.nw, a.nw_mode, i);
+          a.hn[t * D + i] = v;
+          if (a.ha != nullptr) act_store<AT>(reinterpret_cast<AT*>(a.ha) + t * D + i, v);
+        }
+      }
     }
   }
   if (a.xa != nullptr) {
@@ -409,6 +452,11 @@ __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ 
 //   delta rule: S_j <- g S_j;  u_j = beta (v_j - k . S_j);  S_j <- S_j + k u_j;  o_j = q . S_j
 //               with a = k . S_j and b = q . S_j taken on the OLD column: u_j = beta (v_j - g a), o_j = g b + (q . k) u_j
 //   HGRN2:      S_j <- f * S_j + (1 - f) v_j;  o_j = q . S_j      (f per row, in the k slot of the inputs)
+//   general delta rule (decay w and removal rate a per row, unit key u):
+//               S_j <- w * S_j - (a * u) (u . S_j) + k v_j;  o_j = r . S_j
+//               with a = u . S_j and b = (r * w) . S_j on the OLD column: o_j = b - (r . (a * u)) a + (r . k) v_j
+//               (five row vectors per step: r * w, u, w, a * u, k; the two scalars in the beta / decay slots)
+//   lightning:  S_j <- decay S_j + k v_j;  o_j = q . S_j          (one constant decay per head)
 // LPC lanes (4, 8 or 16) own one column: lane `sub` holds the rows of the 16-byte chunks sub, sub + LPC, ... (NCH chunks,
 // rows beyond dk are zero), so a dot product over the rows ends in log2(LPC) shuffles and a warp carries 32 / LPC
 // columns.  More lanes per column mean more blocks and shorter per-step chains (one long sequence), fewer mean fewer
@@ -416,14 +464,17 @@ __global__ void __launch_bounds__(256) hy_delta_prep_kernel(float* __restrict__ 
 // steps (q, k or f, the block's v columns, and for the delta rule beta, decay and q . k) arrive in shared memory by
 // cp.async, one chunk of steps ahead of the arithmetic.
 // grid (n_seqs, H, ceil(dv * LPC / 128)), 128 threads; state [slot][H][dv][dk] fp32;
-// dynamic shared memory 2 * HY_TS * (8 * LPC * NCH + 128 / LPC + 4) floats.
+// dynamic shared memory 2 * HY_TS * (NV * 4 * LPC * NCH + 128 / LPC + 4) floats, NV = hy_rec_vectors(MODE) row vectors per step.
+__host__ __device__ constexpr int hy_rec_vectors(int mode) { return mode == HY_REC_GDELTA ? 5 : 2; }
 #define HY_TS 16
 struct RecurIn {
   const float* c;        // [T, ldc] prepared inputs
   long long ldc;
   long long qoff, koff, voff;   // columns of head 0's q, k (or f) and v; heads follow at q_stride / k_stride / dv
-  int q_heads;           // delta rule: heads share q / k in groups (q head = h / (H / q_heads)); HGRN2: = H
-  const float *beta, *decay, *qk;   // delta rule: [T, H], [T, H], [T, q_heads]
+  long long xoff[3];     // HY_REC_GDELTA: columns of head 0's decay w, removal a*u and key k (qoff: r*w, koff: unit key u)
+  int q_heads;           // delta rule: heads share q / k in groups (q head = h / (H / q_heads)); others: = H
+  const float *beta, *decay, *qk;   // gated delta rule: [T, H], [T, H], [T, q_heads]; HY_REC_GDELTA: beta = r.(a*u), decay = r.k, [T, H]
+  const float* hdecay;   // HY_REC_LIGHTNING: [H] constant decay per head
 };
 __device__ __forceinline__ void hy_cp4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -434,14 +485,17 @@ __device__ __forceinline__ void hy_cp16(float* dst, const float* src) {
 __device__ __forceinline__ void hy_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void hy_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int NCH, int LPC, bool DELTA>
+template <int NCH, int LPC, int MODE>
 __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __restrict__ state, long long state_stride, float* __restrict__ o,
                                                        long long ldo, BatchMeta m, int H, int dk, int dv) {
   pdl_wait();   // no early trigger: this kernel runs long on few warps, and blocks of the next kernel parked beside them slow it
   extern __shared__ __align__(16) float stg[];
+  constexpr bool DELTA = MODE == HY_REC_DELTA;
+  constexpr int NV = hy_rec_vectors(MODE);
   constexpr int DKP = 4 * LPC * NCH;            // padded key dim
   constexpr int HY_RC_COLS = 128 / LPC;         // columns of a block
-  constexpr int STRIDE = 2 * DKP + HY_RC_COLS + 4;
+  constexpr int VO = NV * DKP;                  // the block's value columns follow the row vectors, then the step's scalars
+  constexpr int STRIDE = VO + HY_RC_COLS + 4;
   const int s = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & (LPC - 1);
   const int j0 = blockIdx.z * HY_RC_COLS, jl = warp * (32 / LPC) + lane / LPC, j = j0 + jl;
@@ -452,8 +506,15 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
   const float* cq = in.c + in.qoff + (long long)g * dk;
   const float* ck = in.c + in.koff + (long long)g * dk;
   const float* cv = in.c + in.voff + (long long)h * dv + j0;
+  const float* cx[3] = {nullptr, nullptr, nullptr};
+  if (MODE == HY_REC_GDELTA) {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) cx[i] = in.c + in.xoff[i] + (long long)g * dk;
+  }
+  const float hd = MODE == HY_REC_LIGHTNING ? in.hdecay[h] : 0.f;
   // 16-byte copies when every row piece starts on a 16-byte boundary
-  const bool al = ((in.ldc | in.qoff | in.koff | in.voff | dk | dv) & 3) == 0 && (reinterpret_cast<uintptr_t>(in.c) & 15) == 0;
+  bool al = ((in.ldc | in.qoff | in.koff | in.voff | dk | dv) & 3) == 0 && (reinterpret_cast<uintptr_t>(in.c) & 15) == 0;
+  if (MODE == HY_REC_GDELTA) al = al && ((in.xoff[0] | in.xoff[1] | in.xoff[2]) & 3) == 0;
   for (int i = threadIdx.x; i < 2 * HY_TS * STRIDE; i += blockDim.x) stg[i] = 0.f;   // padding rows / columns stay zero
   float* st = state + (long long)sp.slot * state_stride + ((long long)h * dv + (live ? j : 0)) * dk;
   float S[4 * NCH];
@@ -476,24 +537,30 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
   auto stage = [&](int t0, float* buf) {
     const int nt = sp.len - t0 < HY_TS ? sp.len - t0 : HY_TS;
     if (al) {
-      const int dq = dk >> 2, per = 2 * dq + (ncv >> 2);
+      const int dq = dk >> 2, per = NV * dq + (ncv >> 2);
       for (int idx = threadIdx.x; idx < nt * per; idx += blockDim.x) {
         const int ts = idx / per, u = idx - ts * per;
         const long long row = (long long)(sp.start + t0 + ts) * in.ldc;
         float* d = buf + ts * STRIDE;
         if (u < dq) hy_cp16(d + 4 * u, cq + row + 4 * u);
         else if (u < 2 * dq) hy_cp16(d + DKP + 4 * (u - dq), ck + row + 4 * (u - dq));
-        else hy_cp16(d + 2 * DKP + 4 * (u - 2 * dq), cv + row + 4 * (u - 2 * dq));
+        else if (NV > 2 && u < NV * dq) {
+          const int vi = u / dq, uu = u - vi * dq;
+          hy_cp16(d + vi * DKP + 4 * uu, cx[vi - 2] + row + 4 * uu);
+        } else hy_cp16(d + VO + 4 * (u - NV * dq), cv + row + 4 * (u - NV * dq));
       }
     } else {
-      const int per = 2 * dk + ncv;
+      const int per = NV * dk + ncv;
       for (int idx = threadIdx.x; idx < nt * per; idx += blockDim.x) {
         const int ts = idx / per, u = idx - ts * per;
         const long long row = (long long)(sp.start + t0 + ts) * in.ldc;
         float* d = buf + ts * STRIDE;
         if (u < dk) hy_cp4(d + u, cq + row + u);
         else if (u < 2 * dk) hy_cp4(d + DKP + (u - dk), ck + row + (u - dk));
-        else hy_cp4(d + 2 * DKP + (u - 2 * dk), cv + row + (u - 2 * dk));
+        else if (NV > 2 && u < NV * dk) {
+          const int vi = u / dk, uu = u - vi * dk;
+          hy_cp4(d + vi * DKP + uu, cx[vi - 2] + row + uu);
+        } else hy_cp4(d + VO + (u - NV * dk), cv + row + (u - NV * dk));
       }
     }
     if (DELTA) {
@@ -501,7 +568,14 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
         const int ts = idx / 3, u = idx - ts * 3;
         const long long row = sp.start + t0 + ts;
         const float* src = u == 0 ? in.beta + row * H + h : (u == 1 ? in.decay + row * H + h : in.qk + row * in.q_heads + g);
-        hy_cp4(buf + ts * STRIDE + 2 * DKP + HY_RC_COLS + u, src);
+        hy_cp4(buf + ts * STRIDE + VO + HY_RC_COLS + u, src);
+      }
+    }
+    if (MODE == HY_REC_GDELTA) {
+      for (int idx = threadIdx.x; idx < nt * 2; idx += blockDim.x) {
+        const int ts = idx >> 1, u = idx & 1;
+        const long long row = sp.start + t0 + ts;
+        hy_cp4(buf + ts * STRIDE + VO + HY_RC_COLS + u, (u == 0 ? in.beta : in.decay) + row * H + h);
       }
     }
     hy_cp_commit();
@@ -518,8 +592,57 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
     const long long orow0 = (long long)(sp.start + t0) * ldo + (long long)h * dv + j;
     auto step = [&](int ts) {
       const float* sr = buf + ts * STRIDE;
-      const float v = sr[2 * DKP + jl];
-      if (DELTA) {
+      const float v = sr[VO + jl];
+      if (MODE == HY_REC_GDELTA) {
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int r = (ch * LPC + sub) * 4;
+          const float4 q4 = *reinterpret_cast<const float4*>(sr + r);
+          const float4 u4 = *reinterpret_cast<const float4*>(sr + DKP + r);
+          a0 = fmaf(u4.x, S[4 * ch], a0); a1 = fmaf(u4.y, S[4 * ch + 1], a1);
+          a0 = fmaf(u4.z, S[4 * ch + 2], a0); a1 = fmaf(u4.w, S[4 * ch + 3], a1);
+          b0 = fmaf(q4.x, S[4 * ch], b0); b1 = fmaf(q4.y, S[4 * ch + 1], b1);
+          b0 = fmaf(q4.z, S[4 * ch + 2], b0); b1 = fmaf(q4.w, S[4 * ch + 3], b1);
+        }
+        float a = a0 + a1, b = b0 + b1;
+#pragma unroll
+        for (int off = 1; off < LPC; off <<= 1) {
+          a += __shfl_xor_sync(0xffffffffu, a, off);
+          b += __shfl_xor_sync(0xffffffffu, b, off);
+        }
+        const float ra = sr[VO + HY_RC_COLS], rk = sr[VO + HY_RC_COLS + 1];
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int r = (ch * LPC + sub) * 4;
+          const float4 w4 = *reinterpret_cast<const float4*>(sr + 2 * DKP + r);
+          const float4 e4 = *reinterpret_cast<const float4*>(sr + 3 * DKP + r);
+          const float4 k4 = *reinterpret_cast<const float4*>(sr + 4 * DKP + r);
+          S[4 * ch] = fmaf(k4.x, v, fmaf(w4.x, S[4 * ch], -e4.x * a));
+          S[4 * ch + 1] = fmaf(k4.y, v, fmaf(w4.y, S[4 * ch + 1], -e4.y * a));
+          S[4 * ch + 2] = fmaf(k4.z, v, fmaf(w4.z, S[4 * ch + 2], -e4.z * a));
+          S[4 * ch + 3] = fmaf(k4.w, v, fmaf(w4.w, S[4 * ch + 3], -e4.w * a));
+        }
+        if (sub == 0 && live) o[orow0 + (long long)ts * ldo] = fmaf(rk, v, fmaf(-ra, a, b));
+      } else if (MODE == HY_REC_LIGHTNING) {
+        float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int r = (ch * LPC + sub) * 4;
+          const float4 q4 = *reinterpret_cast<const float4*>(sr + r);
+          const float4 k4 = *reinterpret_cast<const float4*>(sr + DKP + r);
+          S[4 * ch] = fmaf(hd, S[4 * ch], k4.x * v);
+          S[4 * ch + 1] = fmaf(hd, S[4 * ch + 1], k4.y * v);
+          S[4 * ch + 2] = fmaf(hd, S[4 * ch + 2], k4.z * v);
+          S[4 * ch + 3] = fmaf(hd, S[4 * ch + 3], k4.w * v);
+          b0 = fmaf(q4.x, S[4 * ch], b0); b1 = fmaf(q4.y, S[4 * ch + 1], b1);
+          b0 = fmaf(q4.z, S[4 * ch + 2], b0); b1 = fmaf(q4.w, S[4 * ch + 3], b1);
+        }
+        float b = b0 + b1;
+#pragma unroll
+        for (int off = 1; off < LPC; off <<= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
+        if (sub == 0 && live) o[orow0 + (long long)ts * ldo] = b;
+      } else if (DELTA) {
         float kv[4 * NCH];
         float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
@@ -539,7 +662,7 @@ __global__ void __launch_bounds__(128) hy_recur_kernel(RecurIn in, float* __rest
           a += __shfl_xor_sync(0xffffffffu, a, off);
           b += __shfl_xor_sync(0xffffffffu, b, off);
         }
-        const float be = sr[2 * DKP + HY_RC_COLS], gd = sr[2 * DKP + HY_RC_COLS + 1], qk = sr[2 * DKP + HY_RC_COLS + 2];
+        const float be = sr[VO + HY_RC_COLS], gd = sr[VO + HY_RC_COLS + 1], qk = sr[VO + HY_RC_COLS + 2];
         const float u = be * (v - gd * a);
 #pragma unroll
         for (int i = 0; i < 4 * NCH; ++i) S[i] = fmaf(kv[i], u, gd * S[i]);
@@ -611,11 +734,13 @@ __global__ void hy_hgrn_prep_kernel(LinOut P, int off_q, int off_f, int off_v, c
 // The recurrence itself runs in hy_recur_kernel<., false> above: f sits where the delta rule has k.
 
 // ----------------------------------------------------------------------------- per-head RMS norm (+ SiLU gate) of a read-out
-// out[t, h*dv + j] = scale * o / rms_over_dv(o) * w[j] * (gate ? silu(P[t, off_gate + h*dv + j]) : 1)
+// out[t, h*dv + j] = scale * o / rms_over_dv(o) * w[h * w_hstride + j] * (gate ? act(P[t, off_gate + h*dv + j]) : 1)
+// w_hstride: 0 = one weight vector for all heads, dv = a vector per head; gate_sigmoid: 0 = SiLU gate, 1 = sigmoid gate.
+// H = 1 with dv = all heads' size norms the concatenated read-out as one vector.
 template <typename AT>
 __global__ void __launch_bounds__(256) hy_head_norm_kernel(const float* __restrict__ o, long long ldo, const float* __restrict__ w,
                                                            LinOut P, int off_gate, float eps, float scale, AT* __restrict__ out,
-                                                           long long ld_out, int H, int dv) {
+                                                           long long ld_out, int H, int dv, int w_hstride, int gate_sigmoid) {
   pdl_launch_dependents();
   pdl_wait();
   const long long t = blockIdx.x;
@@ -627,8 +752,11 @@ __global__ void __launch_bounds__(256) hy_head_norm_kernel(const float* __restri
     ss = warp_sum(ss);
     const float inv = scale / sqrtf(ss / (float)dv + eps);
     for (int j = lane; j < dv; j += 32) {
-      float v = p[j] * inv * w[j];
-      if (off_gate >= 0) v *= hy_silu(lin_at(P, t, off_gate + h * dv + j));
+      float v = p[j] * inv * w[(long long)h * w_hstride + j];
+      if (off_gate >= 0) {
+        const float gz = lin_at(P, t, off_gate + h * dv + j);
+        v *= gate_sigmoid ? hy_sigmoid(gz) : hy_silu(gz);
+      }
       act_store<AT>(out + t * ld_out + (long long)h * dv + j, v);
     }
   }
@@ -697,6 +825,13 @@ template <> __device__ __forceinline__ float hy_dot_row<bf16>(const float* __res
   return d;
 }
 
+// rows that need not start on a 16-byte boundary
+template <typename KT> __device__ __forceinline__ float hy_dot_row_any(const float* __restrict__ q, const KT* __restrict__ kr, int dk) {
+  float d = 0.f;
+  for (int i = 0; i < dk; ++i) d = fmaf(q[i], act_load<KT>(kr + i), d);
+  return d;
+}
+
 // q (bias added) and the output gate of the attention heads as one bf16 row [q | gate] per token: what the tcgen05 attention
 // reads when the projection came back as split-K planes (steps of few rows).  grid (T, ceil((nq + ng) / 256)).
 __global__ void hy_qg_pack_kernel(LinOut P, int off_q, int nq, int off_g, int ng, bf16* __restrict__ out) {
@@ -713,11 +848,13 @@ __global__ void hy_qg_pack_kernel(LinOut P, int off_q, int nq, int off_g, int ng
 // dot with the query in shared memory), the warp does the online softmax, then lanes own value channels for the weighted
 // sum; at the end warp 0 merges the warps' (max, sum, accumulator) triples.  No rotation: positions enter through the
 // mask only.  The epilogue multiplies by sigmoid(gate column) and `out_scale`.
-// dv <= 256.  Dynamic shared memory: (dk rounded up to 4) + warps * (2 + dv) floats.
-template <typename KT, typename AT>
+// dv <= 32 * NACC (NACC = 8 or 16 value channels per lane).  Key / value rows of the pools are ldk / ldv elements apart
+// (ldk = dk, ldv = dv for separate pools; a value that is the head of its key row reads the key pool with ldv = ldk).
+// Dynamic shared memory: (dk rounded up to 4) + warps * (2 + dv) floats.
+template <typename KT, typename AT, int NACC>
 __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q, int off_gate, const KT* __restrict__ k_pool,
                                                              const KT* __restrict__ v_pool, BatchMeta m, int H, int G, int dk, int dv,
-                                                             int window, int keep_first, float scale, float out_scale,
+                                                             int ldk, int ldv, int window, int keep_first, float scale, float out_scale,
                                                              AT* __restrict__ out, long long ld_out) {
   pdl_launch_dependents();
   pdl_wait();
@@ -735,12 +872,12 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
   const int n_first = keep_first < lo ? keep_first : lo;   // kept keys that the window does not already cover
   const int n_vis = n_first + (pos - lo + 1);
   float mx = -INFINITY, l = 0.f;
-  float acc[8];
+  float acc[NACC];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  for (int c = 0; c < NACC; ++c) acc[c] = 0.f;
   // even dv: a lane owns channel pairs (2 * (lane + 32 c), + 1), c < 4, and takes four keys per round so that their value
   // loads are in flight together; odd dv: a lane owns channels lane + 32 c, one key per round
-  const bool pairs = (dv & 1) == 0;
+  const bool pairs = ((dv | ldv) & 1) == 0;
   for (int base = warp * 32; base < n_vis; base += nw * 32) {
     const int idx = base + lane;
     float sc = -INFINITY;
@@ -748,7 +885,7 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
     if (idx < n_vis) {
       const int kp = idx < n_first ? idx : lo + (idx - n_first);
       prow = ((long long)pages[kp / m.page_tokens] * G + g) * m.page_tokens + kp % m.page_tokens;
-      sc = hy_dot_row<KT>(q, k_pool + prow * dk, dk);
+      sc = (ldk & 7) == 0 ? hy_dot_row<KT>(q, k_pool + prow * ldk, dk) : hy_dot_row_any<KT>(q, k_pool + prow * ldk, dk);
     }
     const float tmax = warp_max(sc);
     const float nm = fmaxf(mx, tmax);
@@ -756,20 +893,20 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
     const float p = idx < n_vis ? expf(sc - nm) : 0.f;
     l = l * corr + warp_sum(p);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] *= corr;
+    for (int c = 0; c < NACC; ++c) acc[c] *= corr;
     mx = nm;
     const int cnt = n_vis - base < 32 ? n_vis - base : 32;
     if (pairs) {
       for (int jj = 0; jj < cnt; jj += 4) {   // lanes past cnt hold p = 0 and row 0 of the pool (finite values)
         float pj[4];
-        float2 vv[4][4];
+        float2 vv[4][NACC / 2];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           pj[u] = __shfl_sync(0xffffffffu, p, jj + u);
           const long long pr = __shfl_sync(0xffffffffu, prow, jj + u);
-          const KT* vr = v_pool + pr * dv;
+          const KT* vr = v_pool + pr * ldv;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < NACC / 2; ++c) {
             const int d = 2 * (lane + 32 * c);
             vv[u][c] = (64 * c < dv && d < dv) ? act_load2<KT>(vr + d) : make_float2(0.f, 0.f);
           }
@@ -777,7 +914,7 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
 #pragma unroll
         for (int u = 0; u < 4; ++u)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < NACC / 2; ++c) {
             if (64 * c >= dv) continue;
             acc[2 * c] = fmaf(pj[u], vv[u][c].x, acc[2 * c]);
             acc[2 * c + 1] = fmaf(pj[u], vv[u][c].y, acc[2 * c + 1]);
@@ -787,9 +924,9 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
       for (int jj = 0; jj < cnt; ++jj) {
         const float pj = __shfl_sync(0xffffffffu, p, jj);
         const long long pr = __shfl_sync(0xffffffffu, prow, jj);
-        const KT* vr = v_pool + pr * dv;
+        const KT* vr = v_pool + pr * ldv;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < NACC; ++c) {
           const int d = lane + 32 * c;
           if (d < dv) acc[c] = fmaf(pj, act_load<KT>(vr + d), acc[c]);
         }
@@ -800,13 +937,13 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
   if (lane == 0) { mine[0] = mx; mine[1] = l; }
   if (pairs) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < NACC / 2; ++c) {
       const int d = 2 * (lane + 32 * c);
       if (d < dv) { mine[2 + d] = acc[2 * c]; mine[3 + d] = acc[2 * c + 1]; }
     }
   } else {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < NACC; ++c) {
       const int d = lane + 32 * c;
       if (d < dv) mine[2 + d] = acc[c];
     }
@@ -817,20 +954,20 @@ __global__ void __launch_bounds__(512) hy_attn_window_kernel(LinOut P, int off_q
   for (int w = 0; w < nw; ++w) M = fmaxf(M, part[(long long)w * (2 + dv)]);
   float L = 0.f;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  for (int c = 0; c < NACC; ++c) acc[c] = 0.f;
   for (int w = 0; w < nw; ++w) {
     const float* pw = part + (long long)w * (2 + dv);
     const float f = expf(pw[0] - M);     // a warp without keys holds max = -inf: weight 0
     L += pw[1] * f;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < NACC; ++c) {
       const int d = lane + 32 * c;
       if (d < dv) acc[c] = fmaf(pw[2 + d], f, acc[c]);
     }
   }
   const float inv = out_scale / L;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = 0; c < NACC; ++c) {
     const int d = lane + 32 * c;
     if (d < dv) {
       float v = acc[c] * inv;
@@ -974,6 +1111,276 @@ __global__ void hy_logits_kernel(LinOut y, float cap, float* __restrict__ out, i
   const int i = (int)(idx - t * V);
   const float v = lin_at(y, t, i);
   out[idx] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+// ----------------------------------------------------------------------------- latent attention
+// Per token the fused projection P carries q (H heads of [dn unrotated | dr rotated]) and the down-projection
+// [R latent | dr rotated key part].  One block per token:
+//   cache row  = [ latent / rms(latent) * nw  |  rot(key part) ]      -> k_pool (one "key head", row of R + dr elements)
+//   qa[t, h]   = [ (filled by hy_head_mm_t_kernel)  |  rot(q rotated part of head h) ]   fp32, rows of H * (R + dr)
+// rot: entries 2i, 2i+1 (i < rot_dims / 2) turn by the angle pos * freq[i]; the others pass.  Angles are fp32.
+template <typename KT>
+__global__ void __launch_bounds__(256) hy_latent_prep_kernel(LinOut P, int off_q, int off_dkv, int H, int dn, int dr, int R, int rot_dims,
+                                                             const float* __restrict__ freq, const float* __restrict__ nw, float eps,
+                                                             KT* __restrict__ k_pool, BatchMeta m, float* __restrict__ qa) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int s = m.tok_seq[row], pos = m.tok_pos[row];
+  const int page = m.page_table[(long long)m.seq_slot[s] * m.max_pages + pos / m.page_tokens];
+  KT* kr = k_pool + ((long long)page * m.page_tokens + pos % m.page_tokens) * (R + dr);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < R; i += 256) {
+    const float v = lin_at(P, row, off_dkv + i);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum<256>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)R + eps);
+  for (int i = threadIdx.x; i < R; i += 256) act_store<KT>(kr + i, lin_at(P, row, off_dkv + i) * inv * nw[i]);
+  const int half = rot_dims >> 1, hp = dr - half;   // per vector: `half` pairs, then the entries that pass unchanged
+  // vector 0 = the shared key part, 1 + h = head h's rotated query part
+  for (int idx = threadIdx.x; idx < (H + 1) * hp; idx += 256) {
+    const int vec = idx / hp, i = idx - vec * hp;
+    const int src = vec == 0 ? off_dkv + R : off_q + (vec - 1) * (dn + dr) + dn;
+    float* qd = qa + (long long)row * H * (R + dr) + (long long)(vec - 1) * (R + dr) + R;
+    if (i < half) {
+      const float u = lin_at(P, row, src + 2 * i), v = lin_at(P, row, src + 2 * i + 1);
+      float sn, cs;
+      sincosf((float)pos * freq[i], &sn, &cs);
+      const float a = u * cs - v * sn, b = v * cs + u * sn;
+      if (vec == 0) { act_store<KT>(kr + R + 2 * i, a); act_store<KT>(kr + R + 2 * i + 1, b); }
+      else { qd[2 * i] = a; qd[2 * i + 1] = b; }
+    } else {
+      const int j = rot_dims + (i - half);
+      const float v = lin_at(P, row, src + j);
+      if (vec == 0) act_store<KT>(kr + R + j, v);
+      else qd[j] = v;
+    }
+  }
+}
+
+// Per-head products with a weight that is stored head by head.
+// "t" form (a query folded into the latent space): y[t, h * ldy + n] = sum_k X[t, xoff + h * xs + k] * W[(h * K + k) * N + n]
+// grid (ceil(T / 8), H), 256 threads over n; the 8 rows' inputs sit in shared memory (8 * K floats).
+#define HY_MM_ROWS 8
+__global__ void __launch_bounds__(256) hy_head_mm_t_kernel(LinOut X, int xoff, int xs, const bf16* __restrict__ W, float* __restrict__ y,
+                                                           long long ldy_row, int ldy, int T, int K, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float xsm[];
+  const int t0 = blockIdx.x * HY_MM_ROWS, h = blockIdx.y;
+  const int nt = T - t0 < HY_MM_ROWS ? T - t0 : HY_MM_ROWS;
+  for (int i = threadIdx.x; i < HY_MM_ROWS * K; i += 256) {
+    const int r = i / K, k = i - r * K;
+    xsm[i] = r < nt ? lin_at(X, t0 + r, xoff + h * xs + k) : 0.f;
+  }
+  __syncthreads();
+  const bf16* Wh = W + (long long)h * K * N;
+  for (int n = threadIdx.x; n < N; n += 256) {
+    float acc[HY_MM_ROWS];
+#pragma unroll
+    for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const float w = bf2f(Wh[(long long)k * N + n]);
+#pragma unroll
+      for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = fmaf(xsm[r * K + k], w, acc[r]);
+    }
+    for (int r = 0; r < nt; ++r) y[(long long)(t0 + r) * ldy_row + (long long)h * ldy + n] = acc[r];
+  }
+}
+// plain form (a latent read-out turned into the head's value): y[t, h * N + n] = sum_k x[t, h * K + k] * W[(h * N + n) * K + k]
+// grid (ceil(T / 8), H), 256 threads: a warp per output n, lanes over k.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_head_mm_kernel(const float* __restrict__ x, long long ldx, const bf16* __restrict__ W,
+                                                         AT* __restrict__ y, long long ldy, int T, int K, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float xsm[];
+  const int t0 = blockIdx.x * HY_MM_ROWS, h = blockIdx.y;
+  const int nt = T - t0 < HY_MM_ROWS ? T - t0 : HY_MM_ROWS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < HY_MM_ROWS * K; i += 256) {
+    const int r = i / K, k = i - r * K;
+    xsm[i] = r < nt ? x[(long long)(t0 + r) * ldx + (long long)h * K + k] : 0.f;
+  }
+  __syncthreads();
+  for (int n = warp; n < N; n += 8) {
+    const bf16* wr = W + ((long long)h * N + n) * K;
+    float acc[HY_MM_ROWS];
+#pragma unroll
+    for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float w = bf2f(wr[k]);
+#pragma unroll
+      for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = fmaf(xsm[r * K + k], w, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < HY_MM_ROWS; ++r) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && r < nt) act_store<AT>(y + (long long)(t0 + r) * ldy + (long long)h * N + n, v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- element-wise activations of projection columns
+// out[t, i] = act(P[t, off + i]), i < n.  act: 0 SiLU, 1 tanh.  grid (T, ceil(n / 256)).
+template <typename OT>
+__global__ void hy_act_cols_kernel(LinOut P, int off, int n, int act, OT* __restrict__ out, long long ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float z = lin_at(P, t, off + i);
+  act_store<OT>(out + t * ld_out + i, act == 0 ? hy_silu(z) : tanhf(z));
+}
+
+// ----------------------------------------------------------------------------- general delta rule: what the recurrence reads
+// From the fused projection P (r | k | v | gate | a | first decay projection) and the decay's second projection Wd, per
+// token and head (n = key size = value size), all fp32:
+//   w = exp(-e^-1/2 * sigmoid(Wd + w0)),  a = sigmoid(P_a)  (its bias comes with P),  u = k / sqrt(sum k^2 + 1e-6)
+//   c row = [ r * w | u | w | a * u | k | v ] (six blocks of H * n),  ra = r . (a * u),  rk = r . k
+// grid (T), a warp per head.
+__global__ void __launch_bounds__(256) hy_gdelta_prep_kernel(LinOut P, int off_r, int off_k, int off_v, int off_a, LinOut Wd,
+                                                             const float* __restrict__ w0, float* __restrict__ c, long long ldc,
+                                                             float* __restrict__ ra, float* __restrict__ rk, int H, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const long long HN = (long long)H * n;
+  float* row = c + t * ldc;
+  for (int h = warp; h < H; h += nw) {
+    const int b = h * n;
+    float sk = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float k = lin_at(P, t, off_k + b + i);
+      sk = fmaf(k, k, sk);
+    }
+    sk = warp_sum(sk);
+    const float ik = 1.0f / sqrtf(sk + 1e-6f);
+    float s_ra = 0.f, s_rk = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float r = lin_at(P, t, off_r + b + i), k = lin_at(P, t, off_k + b + i);
+      const float w = expf(-0.6065306597126334f * hy_sigmoid(lin_at(Wd, t, b + i) + w0[b + i]));
+      const float a = hy_sigmoid(lin_at(P, t, off_a + b + i));
+      const float u = k * ik, au = a * u;
+      row[b + i] = r * w;
+      row[HN + b + i] = u;
+      row[2 * HN + b + i] = w;
+      row[3 * HN + b + i] = au;
+      row[4 * HN + b + i] = k;
+      row[5 * HN + b + i] = lin_at(P, t, off_v + b + i);
+      s_ra = fmaf(r, au, s_ra);
+      s_rk = fmaf(r, k, s_rk);
+    }
+    s_ra = warp_sum(s_ra);
+    s_rk = warp_sum(s_rk);
+    if (lane == 0) { ra[t * H + h] = s_ra; rk[t * H + h] = s_rk; }
+  }
+}
+
+// ----------------------------------------------------------------------------- clamped gated feed-forward, experts
+__device__ __forceinline__ float hy_glu_clamp(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * hy_sigmoid(1.702f * g) * (u + 1.0f);
+}
+// U carries [gate (F) | up (F)] (biases on read): out[t, i] = glu(gate_i, up_i).  grid over T * F.
+template <typename AT>
+__global__ void hy_glu_clamp_kernel(LinOut U, int F, float limit, AT* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * F) return;
+  const long long t = idx / F;
+  const int i = (int)(idx - t * F);
+  act_store<AT>(out + t * ld_out + i, hy_glu_clamp(lin_at(U, t, i), lin_at(U, t, F + i), limit));
+}
+
+// Router: logits z [T, E] (fp32) -> dense weights gw [T, E], zero for experts a token does not use.
+// scores = sigmoid(z); with groups > 0 the experts form `groups` equal groups of neighbours, a group is worth the sum of its
+// two best scores and only experts of the `keep` best groups are eligible; the `top` best eligible experts get
+// score * scale (no renormalisation).  Ties go to the lower index.  One warp per token; shared memory 2 * E + groups floats
+// per warp.
+__global__ void __launch_bounds__(128) hy_route_kernel(LinOut z, int E, int top, int groups, int keep, float scale, float* __restrict__ gw, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float rsm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  float* sc = rsm + (size_t)warp * (2 * E + (groups > 0 ? groups : 1));
+  float* el = sc + E;      // eligible score, or -1 once taken / not eligible
+  float* gs = el + E;
+  for (int e = lane; e < E; e += 32) {
+    const float v = hy_sigmoid(lin_at(z, t, e));
+    sc[e] = v;
+    el[e] = v;
+  }
+  __syncwarp();
+  if (groups > 0 && keep < groups) {
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float b1 = -1.f, b2 = -1.f;
+      for (int i = 0; i < per; ++i) {
+        const float v = sc[g * per + i];
+        if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v;
+      }
+      gs[g] = b1 + (per > 1 ? b2 : 0.f);
+    }
+    __syncwarp();
+    // a group stays when fewer than `keep` groups beat it (a tie counts for the lower index)
+    for (int g = lane; g < groups; g += 32) {
+      int better = 0;
+      for (int o = 0; o < groups; ++o) better += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+      if (better >= keep)
+        for (int i = 0; i < per; ++i) el[g * per + i] = -1.f;
+    }
+    __syncwarp();
+  }
+  for (int e = lane; e < E; e += 32) gw[t * E + e] = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float bv = -1.f;
+    int bi = E;
+    for (int e = lane; e < E; e += 32)
+      if (el[e] > bv) { bv = el[e]; bi = e; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (bi >= E || bv < 0.f) break;
+    if (lane == 0) { gw[t * E + bi] = sc[bi] * scale; el[bi] = -1.f; }
+    __syncwarp();
+  }
+}
+
+// U carries, expert after expert, [gate_e (f) | up_e (f)], then the shared expert's [gate (sf) | up (sf)].
+// out[t, e * f + i] = gw[t, e] * glu(gate, up; limit) (zero for experts the token does not use),
+// out[t, E * f + i] = glu of the shared expert (limit_s): the input of ONE down projection over all experts' columns.
+template <typename AT>
+__global__ void hy_moe_act_kernel(LinOut U, const float* __restrict__ gw, int E, int f, float limit, int sf, float limit_s,
+                                  AT* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int W = E * f + sf;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * W) return;
+  const long long t = idx / W;
+  const int i = (int)(idx - t * W);
+  float v = 0.f;
+  if (i < E * f) {
+    const int e = i / f, j = i - e * f;
+    const float g = gw[t * E + e];
+    if (g != 0.f) v = g * hy_glu_clamp(lin_at(U, t, 2 * e * f + j), lin_at(U, t, 2 * e * f + f + j), limit);
+  } else {
+    const int j = i - E * f;
+    v = hy_glu_clamp(lin_at(U, t, 2 * E * f + j), lin_at(U, t, 2 * E * f + sf + j), limit_s);
+  }
+  act_store<AT>(out + t * ld_out + i, v);
 }
 
 // ----------------------------------------------------------------------------- loader: any supported source type -> fp32 / bf16, strided rows

@@ -28,7 +28,7 @@ _DIRECT_FIELDS = (
 _OPTIONAL_FIELDS = (("attention_dropout", "attn_dropout", 0.0), ("attention_bias", "attn_bias", False), ("hidden_act", "hidden_act", "silu"))
 
 
-HYBRID_ARCHITECTURES = ("Refatar",)
+HYBRID_ARCHITECTURES = ("Refatar", "Bibevik")
 
 
 def is_hybrid(config: dict) -> bool:
@@ -48,6 +48,8 @@ def hybrid_model_config(raw: dict) -> dict:
   arch = raw.get("architecture")
   if arch not in HYBRID_ARCHITECTURES:
     raise ValueError(f"unknown architecture {arch!r}")
+  if arch == "Bibevik":
+    return bibevik_model_config(raw)
   layers = []
   for i, lc in enumerate(raw["layers"]):
     mx, kind = lc["mixer"], lc["type"]
@@ -79,12 +81,96 @@ def hybrid_model_config(raw: dict) -> dict:
   }
 
 
+def _gated_ff(i: int, mlp) -> dict:
+  """The feed-forward part of a parallel-block layer: none, a clamped gated one with biases, or experts of that form."""
+  if mlp is None:
+    return {"ff": 0, "ff_kind": "none"}
+  if mlp["kind"] == "dense":
+    return {"ff": int(mlp["ff"]), "ff_kind": "glu_clamp", "ff_limit": float(mlp["limit"])}
+  if mlp["kind"] == "moe":
+    rt, ex, sh = mlp["router"], mlp["expert"], mlp.get("shared")
+    gr = rt.get("groups")
+    return {"ff": int(ex["ff"]), "ff_kind": "moe", "ff_limit": float(ex["limit"]), "experts": int(rt["experts"]), "top": int(rt["top"]),
+            "groups": int(gr["count"]) if gr else 0, "keep_groups": int(gr["keep"]) if gr else 0, "route_scale": float(rt["scale"]),
+            "shared_ff": int(sh["ff"]) if sh else 0, "shared_limit": float(sh["limit"]) if sh else 0.0}
+  raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+
+
+def bibevik_model_config(raw: dict) -> dict:
+  """A Bibevik ``config.json`` (``width``, ``vocab``, ``embedding.scale``, ``norm.eps``, ``layers`` [{type, mixer, mlp,
+  weights_of?}]) -> the engine's dict.  Layers are parallel blocks (one norm of a single number; mixer and feed-forward read
+  it and their sum joins the stream).  Mixer kinds: ``latent_attention`` {heads, dim, rot_dim, vdim, kv_rank, scale, rot{base,
+  dims}}, ``general_delta`` {heads, dim} (the rank of the decay's first projection comes from the checkpoint's ``w1`` shape,
+  see ``StageRuntime``; the config may name it as ``rank``), ``lightning`` {heads, dim, vdim, decay[heads]}.  A layer with
+  ``weights_of: j`` uses layer j's tensors."""
+  layers = []
+  for i, lc in enumerate(raw["layers"]):
+    mx, kind = lc["mixer"], lc["type"]
+    if kind == "latent_attention":
+      rot = mx.get("rot") or {}
+      lay = {"mixer": "latent", "heads": int(mx["heads"]), "dim": int(mx["dim"]), "rot_dim": int(mx["rot_dim"]), "vdim": int(mx["vdim"]),
+             "kv_rank": int(mx["kv_rank"]), "scale": float(mx["scale"]), "rot_base": float(rot.get("base", 10000.0)),
+             "rot_dims": int(rot.get("dims", mx["rot_dim"]))}
+    elif kind == "general_delta":
+      lay = {"mixer": "gdelta", "heads": int(mx["heads"]), "dim": int(mx["dim"]), "rank": int(mx.get("rank", 0))}
+    elif kind == "lightning":
+      lay = {"mixer": "lightning", "heads": int(mx["heads"]), "dim": int(mx["dim"]), "vdim": int(mx["vdim"]),
+             "decay": [float(v) for v in mx["decay"]]}
+      if len(lay["decay"]) != lay["heads"]:
+        raise ValueError(f"layer {i}: {len(lay['decay'])} decays for {lay['heads']} heads")
+    else:
+      raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    lay.update(_gated_ff(i, lc.get("mlp")))
+    lay["weights_of"] = int(lc["weights_of"]) if lc.get("weights_of") is not None else -1
+    layers.append(lay)
+  return {
+    "family": "hybrid", "architecture": "Bibevik", "block": "parallel", "norm_scalar": True,
+    "embed_scale": float((raw.get("embedding") or {}).get("scale", 1.0)),
+    "embed_dim": int(raw["width"]), "vocab_size": int(raw["vocab"]), "num_layers": len(layers),
+    "max_seq_len": int(raw.get("max_seq_len", 1 << 20)), "norm_eps": float(raw["norm"]["eps"]),
+    "taps": 0, "side_dim": 0, "logit_softcap": 0.0, "layers": layers,
+    "torch_dtype": HF_PRECISION_STR_TO_DTYPE.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16),
+  }
+
+
+def safetensors_shapes(folder: Path) -> dict:
+  """name -> shape of every tensor in the ``*.safetensors`` files of a folder, from the files' headers alone (8 bytes of
+  little-endian length, then that many bytes of JSON)."""
+  import struct
+  shapes = {}
+  for f in sorted(Path(folder).glob("*.safetensors")):
+    with open(f, "rb") as fh:
+      (n,) = struct.unpack("<Q", fh.read(8))
+      header = json.loads(fh.read(n))
+    shapes.update({k: tuple(v["shape"]) for k, v in header.items() if k != "__metadata__"})
+  return shapes
+
+
+def resolve_tensor_sizes(cfg: dict, shapes: dict) -> dict:
+  """Sizes that a hybrid design leaves to the checkpoint: the rank of a general delta rule's first decay projection is the
+  row count of its ``l<i>.mix.w1`` (of the layer that owns the tensors).  ``shapes``: name -> shape."""
+  if not is_hybrid(cfg):
+    return cfg
+  for i, lay in enumerate(cfg["layers"]):
+    if lay.get("mixer") == "gdelta" and not lay.get("rank"):
+      src = lay["weights_of"] if lay.get("weights_of", -1) >= 0 else i
+      name = f"l{src}.mix.w1"
+      if name not in shapes:
+        raise ValueError(f"layer {i}: neither the configuration nor a tensor {name} gives the rank of the decay projection")
+      lay["rank"] = int(shapes[name][0])
+  return cfg
+
+
 def load_model_config(model_config_path: Path) -> dict:
   """Read a ``config.json`` into the flat dict the engine works with: an HF Llama-shaped one, or (key ``architecture``
-  naming a hybrid design) a per-layer description."""
+  naming a hybrid design) a per-layer description; sizes such a design leaves to the checkpoint are taken from the headers of
+  the ``*.safetensors`` files beside it."""
   hf = json.loads(Path(model_config_path).read_text())
   if hf.get("architecture") in HYBRID_ARCHITECTURES:
-    return hybrid_model_config(hf)
+    cfg = hybrid_model_config(hf)
+    if any(lay.get("mixer") == "gdelta" and not lay.get("rank") for lay in cfg["layers"]):
+      resolve_tensor_sizes(cfg, safetensors_shapes(Path(model_config_path).parent))
+    return cfg
   cfg = {ours: hf[theirs] for theirs, ours in _DIRECT_FIELDS}
   cfg.update({ours: hf.get(theirs, default) for theirs, ours, default in _OPTIONAL_FIELDS})
   cfg["head_dim"] = hf.get("head_dim", hf["hidden_size"] // hf["num_attention_heads"])

@@ -81,6 +81,53 @@ _REFATAR_1B = _refatar(2048, 128256, [
   (("delta", {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}, 8192) if i % 2 == 0 else
    ("parallel", _refatar_pair(32, 8, 64, 64, 1024, 4, 16, 128, 128), 8192)) for i in range(16)], taps=4, side=32)
 
+def _bibevik(width, vocab, layers, eps=1e-6):
+  """A Bibevik config.json: layers is a list of (type, mixer, mlp[, weights_of]) entries."""
+  out = []
+  for ent in layers:
+    lay = {"type": ent[0], "mixer": ent[1], "mlp": ent[2]}
+    if len(ent) > 3:
+      lay["weights_of"] = ent[3]
+    out.append(lay)
+  return {"architecture": "Bibevik", "width": width, "vocab": vocab, "embedding": {"scale": width ** 0.5}, "norm": {"eps": eps}, "layers": out}
+
+
+def _latent(heads, dim, rot_dim, vdim, kv_rank, base=10000.0):
+  return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5,
+          "rot": {"base": base, "dims": rot_dim}}
+
+
+def _glu(ff, limit=7.0):
+  return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def _experts(n, top, ff, groups, keep, shared_ff, scale=1.0, limit=7.0):
+  m = {"kind": "moe", "expert": {"ff": ff, "limit": limit},
+       "router": {"experts": n, "top": top, "scale": scale, "groups": {"count": groups, "keep": keep}}}
+  if shared_ff:
+    m["shared"] = {"ff": shared_ff, "limit": limit}
+  return m
+
+
+def _head_decays(heads):
+  return [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(heads - 1, 1)) for h in range(heads)]
+
+
+_BIBEVIK_TINY = _bibevik(160, 384, [
+  ("lightning", {"heads": 4, "dim": 16, "vdim": 24, "decay": [0.5, 0.9, 0.97, 0.995]}, _glu(320, 1.5)),
+  ("latent_attention", _latent(5, 24, 16, 40, 48), _experts(8, 2, 48, 4, 2, 64, scale=1.5, limit=2.0)),
+  ("general_delta", {"heads": 5, "dim": 32, "rank": 8}, None),
+  ("latent_attention", _latent(5, 24, 16, 40, 48), _experts(8, 2, 48, 4, 2, 64, scale=1.5, limit=2.0), 1),
+  ("general_delta", {"heads": 5, "dim": 32, "rank": 8}, _glu(256, 1.0)),
+])
+# 1B-class geometry for throughput runs (random weights): the widths of llama-3.2-1b, mixers in the order delta rule,
+# latent attention, lightning, latent attention; dense and expert feed-forwards alternate
+_BIBEVIK_1B = _bibevik(2048, 128256, [
+  (("general_delta", {"heads": 32, "dim": 64, "rank": 64}, _glu(8192)) if i % 4 == 0 else
+   ("lightning", {"heads": 16, "dim": 128, "vdim": 128, "decay": _head_decays(16)}, _glu(8192)) if i % 4 == 2 else
+   ("latent_attention", _latent(16, 64, 64, 128, 256, base=500000.0), _experts(16, 4, 1024, 4, 2, 2048)))
+  for i in range(16)])
+
 # model id -> {layers, repo:{EngineClassName: hf repo}, hf_config}
 model_cards = {
   "llama-3.2-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "unsloth/Llama-3.2-1B-Instruct"},
@@ -102,6 +149,8 @@ model_cards = {
                     "hf_config": _qwen(384, 6, 2, 768, 4, vocab=1536, max_pos=4096)},
   "refatar-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/refatar-tiny"}, "hf_config": _REFATAR_TINY},
   "refatar-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/refatar-1b"}, "hf_config": _REFATAR_1B},
+  "bibevik-tiny": {"layers": 5, "repo": {ENGINE_CLASS_NAME: "synthetic/bibevik-tiny"}, "hf_config": _BIBEVIK_TINY},
+  "bibevik-1b": {"layers": 16, "repo": {ENGINE_CLASS_NAME: "synthetic/bibevik-1b"}, "hf_config": _BIBEVIK_1B},
   "mistral-tiny": {"layers": 4, "repo": {ENGINE_CLASS_NAME: "synthetic/mistral-tiny"},
                    "hf_config": _mistral(320, 5, 1, 640, 4, head_dim=64, vocab=1280)},
 }

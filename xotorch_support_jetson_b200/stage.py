@@ -128,7 +128,25 @@ class StageRuntime:
     for i, lc in enumerate(config["layers"]):
       L = lays[i]
       L.ff = lc["ff"]
-      if lc["mixer"] == "delta":
+      L.weights_of = lc.get("weights_of", -1)
+      L.ff_kind = {"relu2": _cabi.FF_RELU2, "none": _cabi.FF_RELU2, "glu_clamp": _cabi.FF_GLU_CLAMP, "moe": _cabi.FF_MOE}[lc.get("ff_kind", "relu2")]
+      L.ff_limit = lc.get("ff_limit", 0.0)
+      if lc.get("ff_kind") == "moe":
+        L.n_experts, L.top, L.groups, L.keep_groups = lc["experts"], lc["top"], lc["groups"], lc["keep_groups"]
+        L.route_scale, L.shared_ff, L.shared_limit = lc["route_scale"], lc["shared_ff"], lc["shared_limit"]
+      if lc["mixer"] in ("latent", "gdelta", "lightning"):
+        L.mixer = {"latent": _cabi.MIX_LATENT, "gdelta": _cabi.MIX_GDELTA, "lightning": _cabi.MIX_LIGHTNING}[lc["mixer"]]
+        L.m_heads, L.m_dim = lc["heads"], lc["dim"]
+        if lc["mixer"] == "latent":
+          L.m_vdim, L.m_rot_dim, L.m_kv_rank, L.m_rot_dims = lc["vdim"], lc["rot_dim"], lc["kv_rank"], lc["rot_dims"]
+          L.m_scale, L.m_rot_base = lc["scale"], lc["rot_base"]
+        elif lc["mixer"] == "gdelta":
+          if not lc.get("rank"):
+            raise ValueError(f"layer {i}: the rank of the decay projection is unknown (model_config.resolve_tensor_sizes)")
+          L.m_vdim, L.m_rank = lc["dim"], lc["rank"]
+        else:
+          L.m_vdim = lc["vdim"]
+      elif lc["mixer"] == "delta":
         L.mixer = _cabi.MIX_DELTA
         L.d_heads, L.d_kv_heads, L.d_dim, L.d_vdim, L.d_taps = lc["heads"], lc["kv_heads"], lc["dim"], lc["vdim"], lc["taps"]
       else:
@@ -141,7 +159,9 @@ class StageRuntime:
     d = _cabi.hybrid_desc(
       n_layers=nl, dim=config["embed_dim"], vocab=config["vocab_size"], taps=config["taps"], side_dim=config["side_dim"],
       norm_eps=config["norm_eps"], logit_softcap=config["logit_softcap"], compute_fp32=int(dtype == "float32"),
-      max_batch_tokens=max_batch_tokens, max_seqs=max_seqs, max_logit_rows=self.max_logit_rows)
+      max_batch_tokens=max_batch_tokens, max_seqs=max_seqs, max_logit_rows=self.max_logit_rows,
+      block=_cabi.BLOCK_PARALLEL if config.get("block") == "parallel" else _cabi.BLOCK_SANDWICH,
+      norm_scalar=int(bool(config.get("norm_scalar", False))), embed_scale=float(config.get("embed_scale", 1.0)))
     self.first_from_mlp = self.last_to_attn = False
     self.is_first = self.is_last = True
     self.desc, self._layers = d, lays
@@ -153,6 +173,10 @@ class StageRuntime:
     self.ho_geometry = self.ho_handles = None
     self.ho_connected = False
     self.ho_sent = {}
+    # per-head constants that the configuration carries enter the engine like tensors
+    for i, lc in enumerate(config["layers"]):
+      if lc["mixer"] == "lightning" and lc.get("weights_of", -1) < 0:
+        self.load_named(f"l{i}.mix.decay", torch.tensor(lc["decay"], dtype=torch.float32))
 
   def load_named(self, name: str, t: torch.Tensor):
     """One tensor of a hybrid model by its checkpoint name (xb_load_named)."""

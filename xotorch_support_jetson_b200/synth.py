@@ -142,6 +142,72 @@ def random_refatar_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bf
   return out
 
 
+def bibevik_param_shapes(cfg: dict, rank: int = 16) -> Dict[str, tuple]:
+  """Tensor names and shapes of a Bibevik checkpoint for its ``config.json`` (Linear weights are [out, in]; layers with
+  ``weights_of`` have no tensors).  ``rank``: rows of a general delta rule's first decay projection where the mixer's entry
+  does not name it (the design leaves that size to the checkpoint)."""
+  D, V = cfg["width"], cfg["vocab"]
+  sh = {"embed": (V, D), "final.norm": (), "head": (V, D)}
+  for i, lc in enumerate(cfg["layers"]):
+    if lc.get("weights_of") is not None:
+      continue
+    p, m = f"l{i}.", lc["mixer"]
+    sh[p + "norm1"] = ()
+    H, n = m["heads"], m["dim"]
+    if lc["type"] == "latent_attention":
+      dr, dv, R = m["rot_dim"], m["vdim"], m["kv_rank"]
+      sh.update({p + "mix.q": (H * (n + dr), D), p + "mix.dkv": (R + dr, D), p + "mix.dkv.norm": (R,), p + "mix.uk": (H * n, R),
+                 p + "mix.uv": (H * dv, R), p + "mix.o": (D, H * dv)})
+    elif lc["type"] == "general_delta":
+      rk = m.get("rank", rank)
+      sh.update({p + "mix." + k: (H * n, D) for k in ("r", "k", "v", "g", "a")})
+      sh.update({p + "mix.a.b": (H * n,), p + "mix.w1": (rk, D), p + "mix.w2": (H * n, rk), p + "mix.w0": (H * n,),
+                 p + "mix.norm": (H * n,), p + "mix.o": (D, H * n)})
+    else:
+      dv = m["vdim"]
+      sh.update({p + "mix.q": (H * n, D), p + "mix.k": (H * n, D), p + "mix.v": (H * dv, D), p + "mix.g": (H * dv, D),
+                 p + "mix.norm": (H * dv,), p + "mix.o": (D, H * dv)})
+    mlp = lc.get("mlp")
+    if mlp and mlp["kind"] == "dense":
+      F = mlp["ff"]
+      sh.update({p + "mlp.gate": (F, D), p + "mlp.gate.b": (F,), p + "mlp.up": (F, D), p + "mlp.up.b": (F,),
+                 p + "mlp.down": (D, F), p + "mlp.down.b": (D,)})
+    elif mlp:
+      F = mlp["expert"]["ff"]
+      sh[p + "mlp.router"] = (mlp["router"]["experts"], D)
+      for e in range(mlp["router"]["experts"]):
+        sh.update({f"{p}mlp.e{e}.gate": (F, D), f"{p}mlp.e{e}.up": (F, D), f"{p}mlp.e{e}.down": (D, F)})
+      if mlp.get("shared"):
+        S = mlp["shared"]["ff"]
+        sh.update({p + "mlp.shared.gate": (S, D), p + "mlp.shared.up": (S, D), p + "mlp.shared.down": (D, S)})
+  return sh
+
+
+def random_bibevik_state(cfg: dict, seed: int = 0, dtype: torch.dtype = torch.bfloat16, gain: float = 1.0, device: str = "cpu",
+                         rank: int = 16) -> Dict[str, torch.Tensor]:
+  """Seeded random Bibevik weights: matrices N(0, gain^2 / in), the stream's one-number norms near 1, vector norm weights
+  1 + N(0, 0.1^2), biases and decay offsets N(0, 0.5^2), embedding rows N(0, 1 / width) (the design scales them up again)."""
+  out = {}
+  for idx, (name, shape) in enumerate(sorted(bibevik_param_shapes(cfg, rank).items())):
+    g = torch.Generator(device=device).manual_seed(seed * 1000003 + idx)
+    rn = lambda: torch.randn(shape, generator=g, device=device)  # noqa: E731
+    leaf = name.split(".")[-1]
+    if leaf == "norm1" or name == "final.norm":
+      t = 1.0 + 0.2 * rn()
+    elif leaf == "norm":
+      t = 1.0 + 0.1 * rn()
+    elif leaf in ("b", "w0"):
+      t = 0.5 * rn()
+    elif name == "embed":
+      t = rn() / (shape[-1] ** 0.5)
+    elif leaf == "router":
+      t = 2.0 * gain * rn() / (shape[-1] ** 0.5)
+    else:
+      t = gain * rn() / (shape[-1] ** 0.5)
+    out[name] = t.to(dtype)
+  return out
+
+
 def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0.02,
                             norm_jitter: float = 0.0, shard_bytes: int = 4 << 30,
                             peaked_head: float = 0.0) -> Path:
@@ -152,6 +218,8 @@ def write_random_checkpoint(path: Path, cfg: dict, seed: int = 0, std: float = 0
     json.dump(cfg, f, indent=1)
   if cfg.get("architecture") == "Refatar":
     state = random_refatar_state(cfg, seed=seed)
+  elif cfg.get("architecture") == "Bibevik":
+    state = random_bibevik_state(cfg, seed=seed)
   else:
     state = random_hf_state(cfg, seed=seed, std=std, norm_jitter=norm_jitter, peaked_head=peaked_head)
   files, cur, cur_bytes = [], {}, 0
