@@ -369,6 +369,51 @@ def test_bf16_prompt_kernels_equal_token_by_token(lib):
   assert rel(single, whole[150:]) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("form", ["0", "2", "4"])
+def test_latent_attention_forms_in_bf16(lib, monkeypatch, form):
+  """bf16 serving runs latent attention on the tensor cores, rows = (token, head) pairs over shared 64-key tiles: four warps of
+  rows per block for prompts ("4"), one warp per block and every sequence's keys shared out over blocks for steps of few rows
+  ("2"); "0" is the per-(token, head) kernel.  Each form pinned: a planted far key at 64-key tile borders in a prompt, in
+  portions that start inside a tile, in single tokens, and a batch of three unequal requests whose rows share tiles."""
+  monkeypatch.setenv("XB_HY_LAT_MMA", form)
+  cfg = config([(latent(heads=3, dim=16, rot_dim=16, vdim=24, kv_rank=48, scale=0.5), None), (latent(heads=5, dim=8, rot_dim=8, vdim=8, kv_rank=160), glu(64))],
+               width=64, vocab=50)
+  w = {k: v.float() for k, v in weights(cfg, seed=19).items()}
+  w["embed"][:, 0] = 0.0
+  w["embed"][1] *= 0.2
+  w["embed"][1, 0] = 1.5                       # the planted token: a channel no other token has
+  w["l0.mix.dkv"][0, :] = 0.0
+  w["l0.mix.dkv"][0, 0] = 6.0                  # latent channel 0 of layer 0 reads it
+  w["l0.mix.uk"][0::16, 0] += 3.0
+  w["l0.mix.uv"][:, 0] += 1.0
+  w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+  st = stage(cfg, w, "bfloat16", page=16, cap=512)
+  n = 200
+  for at in (0, 63, 64, 127, 128, 130):
+    ids = [(5 + 3 * i) % 48 + 2 for i in range(n)]
+    ids[at] = 1
+    ref = logits(cfg, w, ids, rounding=bf16_round)
+    whole = run(st, 0, ids, 0)
+    st.release_slot(0)
+    assert rel(whole, ref) < TOL["bfloat16"], (at, "prompt")
+    got = torch.cat([run(st, 0, ids[:70], 0), run(st, 0, ids[70:129], 70), run(st, 0, ids[129:131], 129)] +
+                    [run(st, 0, [t], 131 + i) for i, t in enumerate(ids[131:150])] + [run(st, 0, ids[150:], 150)])
+    st.release_slot(0)
+    assert rel(got, ref) < TOL["bfloat16"], (at, "portions")
+  ids2 = list(ids)
+  ids2[130] = 2
+  assert rel(logits(cfg, w, ids2, rounding=bf16_round)[131:], ref[131:]) > 3 * TOL["bfloat16"]     # the planted key shows
+  a, b, c = toks(70, 50, 7), toks(3, 50, 8), toks(129, 50, 9)
+  ra, rb, rc = (logits(cfg, w, x, rounding=bf16_round) for x in (a, b, c))
+  t1 = torch.tensor(a + b + c, dtype=torch.int32, device="cuda")
+  o1 = st.forward([0, 3, 1], [70, 3, 129], [0, 0, 0], tokens=t1, want_rows=list(range(202))).cpu().double()
+  assert rel(o1[:70], ra) < TOL["bfloat16"] and rel(o1[70:73], rb) < TOL["bfloat16"] and rel(o1[73:], rc) < TOL["bfloat16"]
+  nxt = st.forward([3, 0, 1], [1, 1, 1], [3, 70, 129], tokens=torch.tensor([b[0], a[0], c[0]], dtype=torch.int32, device="cuda")).cpu().double()
+  for row, seq in zip(nxt, (b + b[:1], a + a[:1], c + c[:1])):
+    assert rel(row[None], logits(cfg, w, seq, rounding=bf16_round)[-1:]) < TOL["bfloat16"]
+  st.close()
+
+
 @pytest.mark.parametrize("lanes", ["4", "8", "16"])
 def test_recurrence_lanes_per_column(lib, monkeypatch, lanes):
   """The recurrences spread a state column over 4, 8 or 16 lanes depending on the step's shape; every variant, pinned,

@@ -7,6 +7,10 @@
 #include <set>
 #include <tuple>
 
+// rows x key shares that the split form of the latent attention may write: steps of fewer than num_sms / 2 tiles of 64 rows
+// use it, with at most this many (row, share) pairs
+#define HY_LAT_SPLIT_ROWS 4864
+
 struct HyTarget {
   void* dst = nullptr;
   bool f32 = false;          // destination type: fp32 (vectors, filters) or bf16 (matrices, tables)
@@ -62,6 +66,9 @@ struct HyModel {
   bool finalized = false;
   // steps of few rows are chains of short kernels: their launches overlap (programmatic serialization); prompts run long
   // kernels, where blocks of the next kernel parked on the SMs cost more than the launch gap (measured: +17% per prompt)
+  float* lat_part = nullptr;           // latent attention: (max, sum, accumulator) of every key share [splits][rows][2 + rank]
+  int use_lat_mma = 1;                 // XB_HY_LAT_MMA: 0 = latent attention through the per-(token, head) kernel everywhere (A/B)
+  size_t maxLatR = 0;
   float *qa = nullptr, *gw = nullptr;   // latent attention: queries in the cache's space [T, H * (rank + rot)]; experts: weights [T, E]
   void* ah = nullptr;                  // parallel blocks: the normed stream as a Linear input (both sublayers read it)
   size_t maxQA = 0, maxE = 0, maxM = 0;   // maxM: widest matrix that passes through the m1 / m2 buffers besides the stream's width
@@ -157,6 +164,7 @@ static int hy_create_mixer(xb_engine* e, int i, bool own, size_t& st, uint64_t& 
     }
     const size_t qa = (size_t)(H * (R + dr)), ol = (size_t)(H * R);
     if (qa > hy->maxQA) hy->maxQA = qa;
+    if ((size_t)R > hy->maxLatR) hy->maxLatR = R;
     if (ol > hy->maxO) hy->maxO = ol;
     kvpos += (uint64_t)(R + dr) * (d.compute_fp32 ? 4 : 2);
   } else if (c.mixer == XB_MIX_GDELTA) {
@@ -455,12 +463,15 @@ static int hy_create(xb_engine* e, const xb_hybrid_desc& d, const xb_hybrid_laye
   XB_TRY(hy_alloc(hy, &hy->head_in, R * D * as));
   if (d.block == XB_BLOCK_PARALLEL) XB_TRY(hy_alloc(hy, &hy->ah, Tm * D * as));
   if (hy->maxQA > 0) XB_TRY(hy_alloc_t(hy, &hy->qa, Tm * hy->maxQA));
+  if (hy->maxLatR > 0 && !d.compute_fp32) XB_TRY(hy_alloc_t(hy, &hy->lat_part, (size_t)HY_LAT_SPLIT_ROWS * (hy->maxLatR + 2)));
   if (hy->maxE > 0) XB_TRY(hy_alloc_t(hy, &hy->gw, Tm * hy->maxE));
   hy->cap_head = R * (size_t)d.vocab * 4 > ws_min ? R * (size_t)d.vocab * 4 : ws_min;
   XB_TRY(hy_alloc(hy, (void**)&hy->head_raw, hy->cap_head));
   {
     const char* g = getenv("XB_HY_TC");
     if (g != nullptr && g[0] == '0') hy->use_tc = 0;
+    const char* lm = getenv("XB_HY_LAT_MMA");
+    if (lm != nullptr) hy->use_lat_mma = atoi(lm);   // 0: off; 1: by the step's shape; 4: always the four-warp unsplit form; 2: always key shares
     const char* ta = getenv("XB_HY_TC_ATTN");
     if (ta != nullptr && ta[0] == '0') hy->use_tc_attn = 0;
     const char* lp = getenv("XB_HY_LPC");
@@ -842,6 +853,45 @@ static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, bool no_span, cons
                        reinterpret_cast<AT*>(hy->a1), (long long)D, st);
 }
 
+// Latent attention through hy_latent_attn_mma_kernel.  0: launched; 1: not applicable (shared memory); < 0: -error.
+template <int WARPS, int DVC>
+static int hy_latent_mma_launch(xb_engine* e, const HyLayer& l, const BatchMeta& m, int T, int n_splits, cudaStream_t st) {
+  HyModel* hy = e->hy;
+  const xb_hybrid_layer& c = l.d;
+  const int H = c.m_heads, R = c.m_kv_rank, W = R + c.m_rot_dim, NR = T * H;
+  const int pitch = ((W + 15) & ~15) + 8;
+  const size_t smem = (size_t)(16 * WARPS + HY_LAT_KEYS) * pitch * sizeof(bf16);
+  if (smem > 200 * 1024) return 1;
+  if (smem > 48 * 1024) {
+    static size_t granted[XB_MAX_DEVICES] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= XB_MAX_DEVICES) return 1;
+    if (granted[dev] < smem) {
+      if (cudaFuncSetAttribute(hy_latent_attn_mma_kernel<WARPS, DVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 1;
+      granted[dev] = 200 * 1024;
+    }
+  }
+  const dim3 grid((NR + 16 * WARPS - 1) / (16 * WARPS), n_splits, (R + DVC - 1) / DVC);
+  if (hy_launch(e, hy_latent_attn_mma_kernel<WARPS, DVC>, grid, dim3(32 * WARPS), smem, st, (const float*)hy->qa, (const bf16*)l.k_pool, m, T, H, W,
+                R, c.m_scale * 1.4426950408889634f, n_splits, hy->lat_part, hy->o, (long long)H * R) != 0)
+    return -1;
+  if (n_splits > 1 &&
+      hy_launch(e, hy_latent_merge_kernel, dim3(NR), dim3(128), 0, st, (const float*)hy->lat_part, n_splits, NR, H, R, hy->o, (long long)H * R) != 0)
+    return -1;
+  return 0;
+}
+static int hy_latent_mma(xb_engine* e, const HyLayer& l, const BatchMeta& m, int T, cudaStream_t st) {
+  const int R = l.d.m_kv_rank, NR = T * l.d.m_heads;
+  const int tiles4 = (NR + 63) / 64, tiles1 = (NR + 15) / 16;
+  const int mode = e->hy->use_lat_mma;
+  if (mode == 4 || (mode != 2 && tiles4 >= e->num_sms / 2)) {   // prompts: four warps of rows per block, every block walks its keys alone
+    return R <= 128 ? hy_latent_mma_launch<4, 128>(e, l, m, T, 1, st) : hy_latent_mma_launch<4, 256>(e, l, m, T, 1, st);
+  }
+  int ns = HY_LAT_SPLIT_ROWS / 16 / tiles1;
+  ns = ns < 1 ? 1 : (ns > 16 ? 16 : ns);
+  return R <= 128 ? hy_latent_mma_launch<1, 128>(e, l, m, T, ns, st) : hy_latent_mma_launch<1, 256>(e, l, m, T, ns, st);
+}
+
 // ----------------------------------------------------------------------------- parallel blocks
 // x <- embed * scale;  per layer: h = norm(x) (made by the previous row op), x += mixer(h) + ff(h).
 // The mixers: latent attention (cache = latent + rotated key part, queries folded into the latent space so that a step
@@ -912,6 +962,14 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       const size_t mm1 = (size_t)HY_MM_ROWS * n * sizeof(float), mm2 = (size_t)HY_MM_ROWS * R * sizeof(float);
       XB_TRY(hy_launch(e, hy_head_mm_t_kernel, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm1, st, P, l.off_q, n + dr,
                        (const bf16*)l.w_uk, hy->qa, (long long)H * W, W, T, n, R));
+      // bf16 serving at sizes the tensor-core tiles take: rows = (token, head) pairs over shared key tiles; steps of few
+      // rows split every sequence's keys over blocks and merge
+      if (std::is_same<AT, bf16>::value && hy->use_lat_mma && W % 8 == 0 && R % 16 == 0) {
+        int rc = hy_latent_mma(e, l, m, T, st);
+        if (rc < 0) return -rc;
+        if (rc == 0) goto latent_done;
+      }
+      {
       const int aw = 16;   // causal: every earlier key is visible
       const size_t asm_bytes = (size_t)(((W + 3) & ~3) + aw * (2 + R)) * sizeof(float);
       const LinOut Q = hy_plain(hy->qa, (long long)H * W);
@@ -922,6 +980,8 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       else
         XB_TRY(hy_launch(e, hy_attn_window_kernel<KT, float, 16>, dim3(T, H), dim3(32 * aw), asm_bytes, st, Q, 0, -1, (const KT*)l.k_pool,
                          (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R));
+      }
+    latent_done:
       XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm2, st, (const float*)hy->o,
                        (long long)H * R, (const bf16*)l.w_uv, a1, (long long)l.n_o, T, R, dv));
     } else if (c.mixer == XB_MIX_GDELTA) {
@@ -929,7 +989,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       LinOut Wd;
       XB_TRY(hy_launch(e, hy_act_cols_kernel<AT>, dim3(T, (rk + 255) / 256), dim3(256), 0, st, P, l.off_w1, rk, 1, a2, (long long)rk));
       XB_TRY(hy_linear<AT>(e, a2, rk, l.w_d2, l.t_d2, nullptr, T, HN, rk, hy->m2, hy->cap_m, st, &Wd));
-      XB_TRY(hy_launch(e, hy_gdelta_prep_kernel, dim3(T), dim3(256), 0, st, P, l.off_r, l.off_k, l.off_v, l.off_a, Wd, (const float*)l.w0,
+      XB_TRY(hy_launch(e, hy_gdelta_prep_kernel, dim3(T, (H + 7) / 8), dim3(256), 0, st, P, l.off_r, l.off_k, l.off_v, l.off_a, Wd, (const float*)l.w0,
                        hy->c, (long long)6 * HN, hy->beta, hy->decay, H, n));
       RecurIn in;
       in.c = hy->c; in.ldc = 6LL * HN; in.qoff = 0; in.koff = HN; in.xoff[0] = 2LL * HN; in.xoff[1] = 3LL * HN; in.xoff[2] = 4LL * HN;
@@ -946,8 +1006,8 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
       in.xoff[0] = in.xoff[1] = in.xoff[2] = 0;
       in.beta = in.decay = in.qk = nullptr; in.hdecay = l.hdecay;
       XB_TRY(hy_recur<HY_REC_LIGHTNING>(e, in, hy->state + l.st_rec, SS, hy->o, (long long)l.n_o, m, n_seqs, H, n, dv, st));
-      XB_TRY(hy_launch(e, hy_head_norm_kernel<AT>, dim3(T, 1), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
-                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, 1.0f, a1, (long long)l.n_o, 1, H * dv, 0, 1));
+      XB_TRY(hy_launch(e, hy_all_heads_norm_kernel<AT>, dim3(T), dim3(256), 0, st, (const float*)hy->o, (long long)l.n_o,
+                       (const float*)l.head_norm, P, l.off_g, d.norm_eps, a1, (long long)l.n_o, H * dv));
     }
     XB_TRY(hy_linear<AT>(e, a1, l.n_o, l.w_o, l.t_o, nullptr, T, D, l.n_o, hy->m1, hy->cap_m, st, &y1));
     if (c.ff > 0) XB_TRY(hy_ff_parallel<AT>(e, l, T, st, &y2));

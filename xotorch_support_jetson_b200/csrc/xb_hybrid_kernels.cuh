@@ -12,6 +12,7 @@
 #pragma once
 #include "xb_common.cuh"
 #include "xb_kernels.cuh"
+#include "xb_latent_attn.cuh"
 #include <math.h>
 
 // Every kernel of the forward opens with griddepcontrol.launch_dependents / griddepcontrol.wait: launched with the
@@ -1223,6 +1224,23 @@ __global__ void __launch_bounds__(256) hy_head_mm_kernel(const float* __restrict
   }
 }
 
+// The read-out of all heads normed as ONE vector (RMS over the n entries of a token), weighted and gated by sigmoid:
+// out[t, i] = o[t, i] / rms(o[t, :]) * w[i] * sigmoid(P[t, off_gate + i]).  grid (T), 256 threads.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_all_heads_norm_kernel(const float* __restrict__ o, long long ldo, const float* __restrict__ w, LinOut P,
+                                                                int off_gate, float eps, AT* __restrict__ out, long long ld_out, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const float* p = o + t * ldo;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += 256) ss = fmaf(p[i], p[i], ss);
+  ss = block_sum<256>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += 256) act_store<AT>(out + t * ld_out + i, p[i] * inv * w[i] * hy_sigmoid(lin_at(P, t, off_gate + i)));
+}
+
 // ----------------------------------------------------------------------------- element-wise activations of projection columns
 // out[t, i] = act(P[t, off + i]), i < n.  act: 0 SiLU, 1 tanh.  grid (T, ceil(n / 256)).
 template <typename OT>
@@ -1241,7 +1259,7 @@ __global__ void hy_act_cols_kernel(LinOut P, int off, int n, int act, OT* __rest
 // token and head (n = key size = value size), all fp32:
 //   w = exp(-e^-1/2 * sigmoid(Wd + w0)),  a = sigmoid(P_a)  (its bias comes with P),  u = k / sqrt(sum k^2 + 1e-6)
 //   c row = [ r * w | u | w | a * u | k | v ] (six blocks of H * n),  ra = r . (a * u),  rk = r . k
-// grid (T), a warp per head.
+// grid (T, ceil(H / 8)), a warp per head.
 __global__ void __launch_bounds__(256) hy_gdelta_prep_kernel(LinOut P, int off_r, int off_k, int off_v, int off_a, LinOut Wd,
                                                              const float* __restrict__ w0, float* __restrict__ c, long long ldc,
                                                              float* __restrict__ ra, float* __restrict__ rk, int H, int n) {
@@ -1251,7 +1269,7 @@ __global__ void __launch_bounds__(256) hy_gdelta_prep_kernel(LinOut P, int off_r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const long long HN = (long long)H * n;
   float* row = c + t * ldc;
-  for (int h = warp; h < H; h += nw) {
+  for (int h = blockIdx.y * nw + warp; h < H; h += nw * gridDim.y) {
     const int b = h * n;
     float sk = 0.f;
     for (int i = lane; i < n; i += 32) {

@@ -125,7 +125,7 @@ _BIBEVIK_TINY = _bibevik(160, 384, [
 _BIBEVIK_1B = _bibevik(2048, 128256, [
   (("general_delta", {"heads": 32, "dim": 64, "rank": 64}, _glu(8192)) if i % 4 == 0 else
    ("lightning", {"heads": 16, "dim": 128, "vdim": 128, "decay": _head_decays(16)}, _glu(8192)) if i % 4 == 2 else
-   ("latent_attention", _latent(16, 64, 64, 128, 256, base=500000.0), _experts(16, 4, 1024, 4, 2, 2048)))
+   ("latent_attention", _latent(16, 64, 64, 128, 256, base=500000.0), _experts(16, 4, 384, 4, 2, 2048)))
   for i in range(16)])
 
 # model id -> {layers, repo:{EngineClassName: hf repo}, hf_config}
