@@ -854,7 +854,7 @@ static int hy_sublayer_input(xb_engine* e, int T, int n_seqs, bool no_span, cons
 }
 
 // Latent attention through hy_latent_attn_mma_kernel.  0: launched; 1: not applicable (shared memory); < 0: -error.
-template <int WARPS, int DVC>
+template <int WARPS, int DVC, int LOADW>
 static int hy_latent_mma_launch(xb_engine* e, const HyLayer& l, const BatchMeta& m, int T, int n_splits, cudaStream_t st) {
   HyModel* hy = e->hy;
   const xb_hybrid_layer& c = l.d;
@@ -867,12 +867,12 @@ static int hy_latent_mma_launch(xb_engine* e, const HyLayer& l, const BatchMeta&
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= XB_MAX_DEVICES) return 1;
     if (granted[dev] < smem) {
-      if (cudaFuncSetAttribute(hy_latent_attn_mma_kernel<WARPS, DVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 1;
+      if (cudaFuncSetAttribute(hy_latent_attn_mma_kernel<WARPS, DVC, LOADW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 1;
       granted[dev] = 200 * 1024;
     }
   }
   const dim3 grid((NR + 16 * WARPS - 1) / (16 * WARPS), n_splits, (R + DVC - 1) / DVC);
-  if (hy_launch(e, hy_latent_attn_mma_kernel<WARPS, DVC>, grid, dim3(32 * WARPS), smem, st, (const float*)hy->qa, (const bf16*)l.k_pool, m, T, H, W,
+  if (hy_launch(e, hy_latent_attn_mma_kernel<WARPS, DVC, LOADW>, grid, dim3(32 * LOADW), smem, st, (const float*)hy->qa, (const bf16*)l.k_pool, m, T, H, W,
                 R, c.m_scale * 1.4426950408889634f, n_splits, hy->lat_part, hy->o, (long long)H * R) != 0)
     return -1;
   if (n_splits > 1 &&
@@ -885,11 +885,11 @@ static int hy_latent_mma(xb_engine* e, const HyLayer& l, const BatchMeta& m, int
   const int tiles4 = (NR + 63) / 64, tiles1 = (NR + 15) / 16;
   const int mode = e->hy->use_lat_mma;
   if (mode == 4 || (mode != 2 && tiles4 >= e->num_sms / 2)) {   // prompts: four warps of rows per block, every block walks its keys alone
-    return R <= 128 ? hy_latent_mma_launch<4, 128>(e, l, m, T, 1, st) : hy_latent_mma_launch<4, 256>(e, l, m, T, 1, st);
+    return R <= 128 ? hy_latent_mma_launch<4, 128, 4>(e, l, m, T, 1, st) : hy_latent_mma_launch<4, 256, 4>(e, l, m, T, 1, st);
   }
   int ns = HY_LAT_SPLIT_ROWS / 16 / tiles1;
-  ns = ns < 1 ? 1 : (ns > 16 ? 16 : ns);
-  return R <= 128 ? hy_latent_mma_launch<1, 128>(e, l, m, T, ns, st) : hy_latent_mma_launch<1, 256>(e, l, m, T, ns, st);
+  ns = ns < 1 ? 1 : (ns > 64 ? 64 : ns);
+  return R <= 128 ? hy_latent_mma_launch<1, 128, 4>(e, l, m, T, ns, st) : hy_latent_mma_launch<1, 256, 4>(e, l, m, T, ns, st);
 }
 
 // ----------------------------------------------------------------------------- parallel blocks
@@ -904,19 +904,32 @@ static int hy_ff_parallel(xb_engine* e, const HyLayer& l, int T, cudaStream_t st
   AT* a2 = reinterpret_cast<AT*>(hy->a2);
   LinOut U;
   XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_up, l.t_up, l.b_up, T, l.n_up, D, hy->P, hy->cap_P, st, &U));
+  // a bf16 matrix out of the tcgen05 Linear (prompts): the activations read and write 16 bytes per thread
+  const bool vec = std::is_same<AT, bf16>::value && U.h != nullptr && U.ld % 8 == 0 && l.n_dn % 8 == 0;
   if (c.ff_kind == XB_FF_GLU_CLAMP) {
     const long long n = (long long)T * c.ff;
-    XB_TRY(hy_launch(e, hy_glu_clamp_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, c.ff, c.ff_limit, a2, (long long)l.n_dn, T));
+    if (vec && c.ff % 8 == 0)
+      XB_TRY(hy_launch(e, hy_glu_clamp_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, U.h, U.ld, U.bias, c.ff, c.ff_limit,
+                       reinterpret_cast<bf16*>(hy->a2), (long long)l.n_dn, T));
+    else
+      XB_TRY(hy_launch(e, hy_glu_clamp_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, c.ff, c.ff_limit, a2, (long long)l.n_dn, T));
   } else {
-    // router in fp32 whatever the serving type: the plain kernels accumulate and store fp32
-    LinOut z;
-    XB_TRY(hy_linear<AT>(e, hy->ah, D, l.w_router, nullptr, nullptr, T, c.n_experts, D, hy->m2, hy->cap_m, st, &z));
+    // router in fp32 whatever the serving type: fp32 accumulation of the products, fp32 logits
+    const int chunks = (c.n_experts + 7) / 8;
+    XB_TRY(hy_launch(e, hy_router_logits_kernel<AT>, dim3((unsigned)(((long long)T * chunks + 7) / 8)), dim3(256), 0, st,
+                     reinterpret_cast<const AT*>(hy->ah), (long long)D, (const bf16*)l.w_router, hy->m2, T, c.n_experts, D));
+    const LinOut z = hy_plain(hy->m2, c.n_experts);
     const size_t rs = (size_t)4 * (2 * c.n_experts + (c.groups > 0 ? c.groups : 1)) * sizeof(float);
     XB_TRY(hy_launch(e, hy_route_kernel, dim3((T + 3) / 4), dim3(128), rs, st, z, c.n_experts, c.top, c.groups, c.keep_groups, c.route_scale,
                      hy->gw, T));
     const long long n = (long long)T * l.n_dn;
-    XB_TRY(hy_launch(e, hy_moe_act_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, (const float*)hy->gw, c.n_experts, c.ff,
-                     c.ff_limit, c.shared_ff > 0 ? c.shared_ff : 0, c.shared_limit, a2, (long long)l.n_dn, T));
+    const int sf = c.shared_ff > 0 ? c.shared_ff : 0;
+    if (vec && c.ff % 8 == 0 && sf % 8 == 0)
+      XB_TRY(hy_launch(e, hy_moe_act_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, U.h, U.ld, (const float*)hy->gw, c.n_experts,
+                       c.ff, c.ff_limit, sf, c.shared_limit, reinterpret_cast<bf16*>(hy->a2), (long long)l.n_dn, T));
+    else
+      XB_TRY(hy_launch(e, hy_moe_act_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, U, (const float*)hy->gw, c.n_experts, c.ff,
+                       c.ff_limit, sf, c.shared_limit, a2, (long long)l.n_dn, T));
   }
   return hy_linear<AT>(e, a2, l.n_dn, l.w_down, l.t_down, l.b_down, T, D, l.n_dn, hy->m2, hy->cap_m, st, y);
 }

@@ -1317,6 +1317,116 @@ __global__ void hy_glu_clamp_kernel(LinOut U, int F, float limit, AT* __restrict
   act_store<AT>(out + t * ld_out + i, hy_glu_clamp(lin_at(U, t, i), lin_at(U, t, F + i), limit));
 }
 
+// The same two activations on a bf16 matrix (prompts: the tcgen05 Linear's output), eight neighbours per thread.
+// F, ld, ld_out and the column offsets are multiples of 8; bias (fp32, added first) may be nullptr.
+__device__ __forceinline__ void hy_load8(const bf16* p, const float* bias, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), d = bf2_to_f2(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  if (bias != nullptr) {
+    const float4 b0 = *reinterpret_cast<const float4*>(bias), b1 = *reinterpret_cast<const float4*>(bias + 4);
+    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w; v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+  }
+}
+__device__ __forceinline__ uint4 hy_glu8(const float* g, const float* u, float limit, float w) {
+  float y[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) y[j] = w * hy_glu_clamp(g[j], u[j], limit);
+  return make_uint4(f2_to_bf2(y[0], y[1]), f2_to_bf2(y[2], y[3]), f2_to_bf2(y[4], y[5]), f2_to_bf2(y[6], y[7]));
+}
+__global__ void hy_glu_clamp_vec_kernel(const bf16* __restrict__ u, long long ld, const float* __restrict__ bias, int F, float limit,
+                                        bf16* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int f8 = F >> 3;
+  if (idx >= (long long)T * f8) return;
+  const long long t = idx / f8;
+  const int i = (int)(idx - t * f8) << 3;
+  float g[8], v[8];
+  hy_load8(u + t * ld + i, bias != nullptr ? bias + i : nullptr, g);
+  hy_load8(u + t * ld + F + i, bias != nullptr ? bias + F + i : nullptr, v);
+  *reinterpret_cast<uint4*>(out + t * ld_out + i) = hy_glu8(g, v, limit, 1.0f);
+}
+__global__ void hy_moe_act_vec_kernel(const bf16* __restrict__ u, long long ld, const float* __restrict__ gw, int E, int f, float limit, int sf,
+                                      float limit_s, bf16* __restrict__ out, long long ld_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int W8 = (E * f + sf) >> 3;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * W8) return;
+  const long long t = idx / W8;
+  const int i = (int)(idx - t * W8) << 3;
+  float g[8], v[8];
+  uint4 r = make_uint4(0u, 0u, 0u, 0u);
+  if (i < E * f) {
+    const int e = i / f, j = i - e * f;
+    const float w = gw[t * E + e];
+    if (w != 0.f) {
+      hy_load8(u + t * ld + 2 * e * f + j, nullptr, g);
+      hy_load8(u + t * ld + 2 * e * f + f + j, nullptr, v);
+      r = hy_glu8(g, v, limit, w);
+    }
+  } else {
+    const int j = i - E * f;
+    hy_load8(u + t * ld + 2 * E * f + j, nullptr, g);
+    hy_load8(u + t * ld + 2 * E * f + sf + j, nullptr, v);
+    r = hy_glu8(g, v, limit_s, 1.0f);
+  }
+  *reinterpret_cast<uint4*>(out + t * ld_out + i) = r;
+}
+
+// Router logits in fp32 for any number of rows: z[t, e] = sum_k x[t, k] w[e, k].  A warp takes one token and up to eight
+// experts: it reads the token's row once and streams eight weight rows (which stay in L1 / L2 across tokens).
+// grid (ceil(T * ceil(E / 8) / 8)), 256 threads.
+template <typename AT>
+__global__ void __launch_bounds__(256) hy_router_logits_kernel(const AT* __restrict__ x, long long ldx, const bf16* __restrict__ w,
+                                                               float* __restrict__ z, int T, int E, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunks = (E + 7) >> 3;
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)T * chunks) return;
+  const long long t = wid / chunks;
+  const int e0 = (int)(wid - t * chunks) << 3;
+  const int ne = E - e0 < 8 ? E - e0 : 8;
+  const AT* xr = x + t * ldx;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if ((K & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int k = lane * 8; k < K; k += 256) {
+      float xv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = act_load<AT>(xr + k + i);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < ne) {
+          const uint4 u = *reinterpret_cast<const uint4*>(w + (long long)(e0 + j) * K + k);
+          const float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), d = bf2_to_f2(u.w);
+          float s = acc[j];
+          s = fmaf(xv[0], a.x, s); s = fmaf(xv[1], a.y, s); s = fmaf(xv[2], b.x, s); s = fmaf(xv[3], b.y, s);
+          s = fmaf(xv[4], c.x, s); s = fmaf(xv[5], c.y, s); s = fmaf(xv[6], d.x, s); s = fmaf(xv[7], d.y, s);
+          acc[j] = s;
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float xv = act_load<AT>(xr + k);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < ne) acc[j] = fmaf(xv, bf2f(w[(long long)(e0 + j) * K + k]), acc[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float v = warp_sum(acc[j]);
+    if (lane == 0 && j < ne) z[t * E + e0 + j] = v;
+  }
+}
+
 // Router: logits z [T, E] (fp32) -> dense weights gw [T, E], zero for experts a token does not use.
 // scores = sigmoid(z); with groups > 0 the experts form `groups` equal groups of neighbours, a group is worth the sum of its
 // two best scores and only experts of the `keep` best groups are eligible; the `top` best eligible experts get

@@ -17,14 +17,15 @@
 #define HY_LAT_KEYS 64
 #define HY_LAT_NEG -1.0e30f
 
-template <int WARPS, int DVC>
-__global__ void __launch_bounds__(32 * WARPS) hy_latent_attn_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ pool, BatchMeta m,
+// LOADW >= WARPS warps per block: all of them stage queries and key tiles, the first WARPS own rows.
+template <int WARPS, int DVC, int LOADW>
+__global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ pool, BatchMeta m,
                                                                         int T, int H, int W, int R, float scale_log2, int n_splits,
                                                                         float* __restrict__ part, float* __restrict__ out, long long ld_out) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char lsm[];
-  constexpr int ROWS = 16 * WARPS, NT = 32 * WARPS, NDV = DVC / 8;
+  constexpr int ROWS = 16 * WARPS, NT = 32 * LOADW, NDV = DVC / 8;
   const int Wp = (W + 15) & ~15, PITCH = Wp + 8;     // bf16 elements per shared row; the 16-byte pad keeps ldmatrix conflict-free
   bf16* Qs = reinterpret_cast<bf16*>(lsm);
   bf16* Ks = Qs + (size_t)ROWS * PITCH;
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(32 * WARPS) hy_latent_attn_mma_kernel(const fl
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int r = r0 + warp * 16 + g + 8 * j;
-    const int t = r < NR ? r / H : -1;
+    const int t = (r < NR && warp < WARPS) ? r / H : -1;
     rpos[j] = t >= 0 ? m.tok_pos[t] : -1;
     rseq[j] = t >= 0 ? m.tok_seq[t] : -1;
   }
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(32 * WARPS) hy_latent_attn_mma_kernel(const fl
     // does this warp hold a row of s
     int wt0 = wr0 / H, wt1 = (wr0 + 15 < NR ? wr0 + 15 : NR - 1) / H;
     bool warp_active = false;
-    if (wr0 < NR)
+    if (wr0 < NR && warp < WARPS)
       for (int t = wt0; t <= wt1; ++t) warp_active = warp_active || m.tok_seq[t] == s;
     for (int kb = k_lo; kb < k_hi; kb += HY_LAT_KEYS) {
       __syncthreads();     // the previous tile (and, first time, the queries) are done with / in place
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(32 * WARPS) hy_latent_attn_mma_kernel(const fl
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int r = r0 + warp * 16 + g + 8 * j;
-    if (r >= NR) continue;
+    if (r >= NR || warp >= WARPS) continue;
     if (n_splits == 1) {
       const int t = r / H, h = r - t * H;
       const float inv = 1.0f / ls[j];
