@@ -995,7 +995,7 @@ static int hy_run_parallel_t(xb_engine* e, int T, int n_seqs, void* const* taps,
                          (const KT*)l.k_pool, m, H, 1, W, R, W, W, far, 0, c.m_scale, 1.0f, hy->o, (long long)H * R));
       }
     latent_done:
-      XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(256), mm2, st, (const float*)hy->o,
+      XB_TRY(hy_launch(e, hy_head_mm_kernel<AT>, dim3((T + HY_MM_ROWS - 1) / HY_MM_ROWS, H), dim3(128), mm2, st, (const float*)hy->o,
                        (long long)H * R, (const bf16*)l.w_uv, a1, (long long)l.n_o, T, R, dv));
     } else if (c.mixer == XB_MIX_GDELTA) {
       const int HN = H * n, rk = c.m_rank;

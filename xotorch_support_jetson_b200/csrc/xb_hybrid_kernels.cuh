@@ -1191,36 +1191,48 @@ __global__ void __launch_bounds__(256) hy_head_mm_t_kernel(LinOut X, int xoff, i
   }
 }
 // plain form (a latent read-out turned into the head's value): y[t, h * N + n] = sum_k x[t, h * K + k] * W[(h * N + n) * K + k]
-// grid (ceil(T / 8), H), 256 threads: a warp per output n, lanes over k.
+// grid (ceil(T / 8), H), 128 threads: a thread owns an output n and walks its weight row 16 bytes at a time against the 8 rows'
+// inputs in shared memory (broadcast reads, no shuffles).
 template <typename AT>
-__global__ void __launch_bounds__(256) hy_head_mm_kernel(const float* __restrict__ x, long long ldx, const bf16* __restrict__ W,
+__global__ void __launch_bounds__(128) hy_head_mm_kernel(const float* __restrict__ x, long long ldx, const bf16* __restrict__ W,
                                                          AT* __restrict__ y, long long ldy, int T, int K, int N) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float xsm[];
   const int t0 = blockIdx.x * HY_MM_ROWS, h = blockIdx.y;
   const int nt = T - t0 < HY_MM_ROWS ? T - t0 : HY_MM_ROWS;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < HY_MM_ROWS * K; i += 256) {
+  for (int i = threadIdx.x; i < HY_MM_ROWS * K; i += 128) {
     const int r = i / K, k = i - r * K;
     xsm[i] = r < nt ? x[(long long)(t0 + r) * ldx + (long long)h * K + k] : 0.f;
   }
   __syncthreads();
-  for (int n = warp; n < N; n += 8) {
+  const bool vec = (K & 7) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+  for (int n = threadIdx.x; n < N; n += 128) {
     const bf16* wr = W + ((long long)h * N + n) * K;
     float acc[HY_MM_ROWS];
 #pragma unroll
     for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float w = bf2f(wr[k]);
+    if (vec) {
+      for (int k = 0; k < K; k += 8) {
+        const uint4 u = *reinterpret_cast<const uint4*>(wr + k);
+        const float2 w0 = bf2_to_f2(u.x), w1 = bf2_to_f2(u.y), w2 = bf2_to_f2(u.z), w3 = bf2_to_f2(u.w);
 #pragma unroll
-      for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = fmaf(xsm[r * K + k], w, acc[r]);
-    }
+        for (int r = 0; r < HY_MM_ROWS; ++r) {
+          const float4 a = *reinterpret_cast<const float4*>(xsm + r * K + k), b = *reinterpret_cast<const float4*>(xsm + r * K + k + 4);
+          float s = acc[r];
+          s = fmaf(a.x, w0.x, s); s = fmaf(a.y, w0.y, s); s = fmaf(a.z, w1.x, s); s = fmaf(a.w, w1.y, s);
+          s = fmaf(b.x, w2.x, s); s = fmaf(b.y, w2.y, s); s = fmaf(b.z, w3.x, s); s = fmaf(b.w, w3.y, s);
+          acc[r] = s;
+        }
+      }
+    } else {
+      for (int k = 0; k < K; ++k) {
+        const float w = bf2f(wr[k]);
 #pragma unroll
-    for (int r = 0; r < HY_MM_ROWS; ++r) {
-      const float v = warp_sum(acc[r]);
-      if (lane == 0 && r < nt) act_store<AT>(y + (long long)(t0 + r) * ldy + (long long)h * N + n, v);
+        for (int r = 0; r < HY_MM_ROWS; ++r) acc[r] = fmaf(xsm[r * K + k], w, acc[r]);
+      }
     }
+    for (int r = 0; r < nt; ++r) act_store<AT>(y + (long long)(t0 + r) * ldy + (long long)h * N + n, acc[r]);
   }
 }
 
