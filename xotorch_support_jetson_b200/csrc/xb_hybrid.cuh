@@ -860,7 +860,7 @@ static int hy_latent_mma_launch(xb_engine* e, const HyLayer& l, const BatchMeta&
   const xb_hybrid_layer& c = l.d;
   const int H = c.m_heads, R = c.m_kv_rank, W = R + c.m_rot_dim, NR = T * H;
   const int pitch = ((W + 15) & ~15) + 8;
-  const size_t smem = (size_t)(16 * WARPS + HY_LAT_KEYS) * pitch * sizeof(bf16);
+  const size_t smem = (size_t)(16 * WARPS + 2 * HY_LAT_KEYS) * pitch * sizeof(bf16);
   if (smem > 200 * 1024) return 1;
   if (smem > 48 * 1024) {
     static size_t granted[XB_MAX_DEVICES] = {0};

@@ -7,15 +7,22 @@
 //   hy_head_mm_t_kernel + hy_latent_prep_kernel), rounded to bf16 in shared memory
 //   pool [n_pages * page_tokens][W] bf16, W = R + rot, W and R multiples of 16
 //   grid (ceil(T * H / (16 * WARPS)), n_splits, ceil(R / DVC)): a block takes the tile's rows, one share of every
-//   sequence's keys (n_splits equal shares, whole 64-key tiles) and DVC value columns
+//   sequence's keys (n_splits equal shares, whole key tiles) and DVC value columns
 //   n_splits == 1: out[t][h * R + c] = O / l;  else part[split][r][2 + R] = (m, l, O) and hy_latent_merge_kernel finishes.
 // A tile's tokens may belong to several sequences (a batch of single tokens): the block walks them one after the other,
 // rows of other sequences are masked for that walk.  Causal: row (t, h) sees keys at positions <= pos(t).
 #pragma once
 #include "xb_attn_mma.cuh"
 
-#define HY_LAT_KEYS 64
+#define HY_LAT_KEYS 32   // keys per shared-memory tile; two tiles are resident (the next one arrives by cp.async while this one is used)
 #define HY_LAT_NEG -1.0e30f
+
+// 16 bytes global -> shared without passing registers; bytes = 0 writes zeros instead (rows and columns outside the cache)
+__device__ __forceinline__ void lat_cp16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lat_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void lat_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // LOADW >= WARPS warps per block: all of them stage queries and key tiles, the first WARPS own rows.
 template <int WARPS, int DVC, int LOADW>
@@ -25,10 +32,10 @@ __global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const fl
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char lsm[];
-  constexpr int ROWS = 16 * WARPS, NT = 32 * LOADW, NDV = DVC / 8;
+  constexpr int ROWS = 16 * WARPS, NT = 32 * LOADW, NDV = DVC / 8, NB = HY_LAT_KEYS / 8, KK = HY_LAT_KEYS / 16;
   const int Wp = (W + 15) & ~15, PITCH = Wp + 8;     // bf16 elements per shared row; the 16-byte pad keeps ldmatrix conflict-free
   bf16* Qs = reinterpret_cast<bf16*>(lsm);
-  bf16* Ks = Qs + (size_t)ROWS * PITCH;
+  bf16* Kbuf = Qs + (size_t)ROWS * PITCH;     // two tiles of HY_LAT_KEYS rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int NR = T * H;
   const int r0 = blockIdx.x * ROWS;
@@ -75,32 +82,42 @@ __global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const fl
     bool warp_active = false;
     if (wr0 < NR && warp < WARPS)
       for (int t = wt0; t <= wt1; ++t) warp_active = warp_active || m.tok_seq[t] == s;
-    for (int kb = k_lo; kb < k_hi; kb += HY_LAT_KEYS) {
-      __syncthreads();     // the previous tile (and, first time, the queries) are done with / in place
-      const int c8 = W >> 3;
+    const int c8 = W >> 3;
+    auto issue = [&](int kb, bf16* buf) {
       for (int i = threadIdx.x; i < HY_LAT_KEYS * (PITCH >> 3); i += NT) {
         const int k = i / (PITCH >> 3), c = i - k * (PITCH >> 3);
         const int kp = kb + k;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (kp < k_hi && c < c8) {
-          const long long prow = (long long)pages[kp / m.page_tokens] * m.page_tokens + kp % m.page_tokens;
-          v = *reinterpret_cast<const uint4*>(pool + prow * W + c * 8);
-        }
-        *reinterpret_cast<uint4*>(Ks + (size_t)k * PITCH + c * 8) = v;
+        const bool ok = kp < k_hi && c < c8;
+        const bf16* src = pool;
+        if (ok) src = pool + ((long long)pages[kp / m.page_tokens] * m.page_tokens + kp % m.page_tokens) * W + c * 8;
+        lat_cp16(smem_u32(buf + (size_t)k * PITCH + c * 8), src, ok ? 16 : 0);
       }
-      __syncthreads();
-      if (!warp_active) continue;
-      // ---- S = Q K^T, 16 rows x 64 keys per warp
-      float sacc[8][4];
+      lat_cp_commit();
+    };
+    __syncthreads();       // nobody still reads a tile of the previous sequence; the queries are in place
+    if (k_lo < k_hi) issue(k_lo, Kbuf);
+    int cur = 0;
+    for (int kb = k_lo; kb < k_hi; kb += HY_LAT_KEYS, cur ^= 1) {
+      bf16* Ks = Kbuf + (size_t)cur * HY_LAT_KEYS * PITCH;
+      if (kb + HY_LAT_KEYS < k_hi) {
+        issue(kb + HY_LAT_KEYS, Kbuf + (size_t)(cur ^ 1) * HY_LAT_KEYS * PITCH);
+        lat_cp_wait<1>();
+      } else {
+        lat_cp_wait<0>();
+      }
+      __syncthreads();     // this tile has arrived for every thread
+      if (warp_active) {
+      // ---- S = Q K^T, 16 rows x HY_LAT_KEYS keys per warp
+      float sacc[NB][4];
 #pragma unroll
-      for (int nb = 0; nb < 8; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+      for (int nb = 0; nb < NB; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
       const uint32_t qaddr = smem_u32(Qs + (size_t)(warp * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8);
       const uint32_t kaddr = smem_u32(Ks + (size_t)((lane & 7) + ((lane >> 4) & 1) * 8) * PITCH + ((lane >> 3) & 1) * 8);
       for (int ks = 0; ks < Wp; ks += 16) {
         uint32_t a[4];
         ldsm_x4(qaddr + ks * 2, a[0], a[1], a[2], a[3]);
 #pragma unroll
-        for (int nb = 0; nb < 8; nb += 2) {
+        for (int nb = 0; nb < NB; nb += 2) {
           uint32_t b0, b1, b2, b3;
           ldsm_x4(kaddr + (uint32_t)(nb * 8 * PITCH + ks) * 2, b0, b1, b2, b3);
           mma_bf16_16816(sacc[nb], a, b0, b1);
@@ -110,7 +127,7 @@ __global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const fl
       // ---- mask, online softmax (fp32, base 2)
       float tmax[2] = {HY_LAT_NEG, HY_LAT_NEG};
 #pragma unroll
-      for (int nb = 0; nb < 8; ++nb)
+      for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = e >> 1, kp = kb + nb * 8 + 2 * q + (e & 1);
@@ -129,9 +146,9 @@ __global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const fl
         mx[j] = nm;
         ls[j] *= corr[j];
       }
-      uint32_t pa[4][4];
+      uint32_t pa[KK][4];
 #pragma unroll
-      for (int nb = 0; nb < 8; ++nb) {
+      for (int nb = 0; nb < NB; ++nb) {
         float p[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -149,7 +166,7 @@ __global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const fl
       // ---- O += P V: V = the latent columns [c0, c0 + DVC) of the same tile
       const uint32_t vaddr = smem_u32(Ks + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + c0 + ((lane >> 4) & 1) * 8);
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
+      for (int kk = 0; kk < KK; ++kk) {
 #pragma unroll
         for (int n = 0; n < NDV; n += 2) {
           if (n < ndv) {
@@ -160,6 +177,8 @@ __global__ void __launch_bounds__(32 * LOADW) hy_latent_attn_mma_kernel(const fl
           }
         }
       }
+      }
+      __syncthreads();     // every warp is done with this tile before the copy after next overwrites it
     }
   }
   // ---- results
