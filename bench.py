@@ -17,7 +17,7 @@ dominant kernel (tcgen05 weight-streaming Linear) against the measured HBM peak;
 `extra` carries decode bs=1 and prefill tok/s with their roofline fractions.
 
 `--impl reference` times the reference's own CPU path (the oracle port -- torchtune is not
-installable here, DESIGN.md) on the same config with a bounded per-step sample.
+installable here) on the same config with a bounded per-step sample.
 """
 import argparse
 import asyncio
@@ -348,7 +348,7 @@ def run_b200(args):
   extra = {"decode_ms_per_step_all_reps": [t / K for t in decode_all], "prefill_tok_s": prefill_tok_s, "prefill_ms": prefill_ms,
            "decode_step_hbm_frac": step_frac, "decode_step_bytes_per_gpu": step_bytes,
            "decode_ctx_avg": ctx_avg}
-  # prefill against the tensor roofline (algorithmic FLOPs, SURVEY 8d)
+  # prefill against the tensor roofline (algorithmic FLOPs)
   D, H, KV, hd, I, V = cfg["embed_dim"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["intermediate_dim"], cfg["vocab_size"]
   nl_total = cfg["num_layers"]
   T_all = B * M * L
@@ -662,7 +662,7 @@ def e2e_engine_api(runner, cfg, prompt, K, W):
   V = cfg["vocab_size"]
   eng.end_request("bench")
 
-  # the same loop kept on the device (generate(): SURVEY 8f.1); rate from the arrival times of the
+  # the same loop kept on the device (generate()); rate from the arrival times of the
   # ids at the host callback, first W steps (and the prefill) excluded
   stamps = []
 

@@ -3,8 +3,7 @@
 TEST INFRASTRUCTURE.  Builds a random-init HF Llama / Qwen2 model from the registered
 tiny configs, feeds the same state dict to ``oracle.torch_oracle`` (through the
 reference's HF->torchtune remap incl. ``_permute``) and compares prefill logits and a
-few cached decode steps.  Run: ``python -m oracle.hf_crosscheck``.  Results are quoted
-in DESIGN.md; tests/test_oracle.py runs the same check.
+few cached decode steps.  Run: ``python -m oracle.hf_crosscheck``; tests/test_oracle.py runs the same check.
 """
 import copy
 import sys

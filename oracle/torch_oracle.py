@@ -4,11 +4,11 @@ TEST INFRASTRUCTURE ONLY -- the product (``xotorch_support_jetson_b200``) never 
 this file.  It is the parity checker for the CUDA path and the timed CPU baseline.
 
 PARITY PINNING STATUS: **parity unpinned by reference fixtures** -- the reference holds
-no golden logits / hidden states / token sequences for this path (SURVEY.md section 8c),
+no golden logits / hidden states / token sequences for this path,
 and its arithmetic lives in ``torchtune>=0.6.1`` (un-vendored, not installable here).
 The pin is therefore (a) the reference's own call sites, restated line by line below,
 (b) an independent cross-check against HuggingFace ``LlamaForCausalLM`` /
-``Qwen2ForCausalLM`` (``oracle/hf_crosscheck.py``; results recorded in DESIGN.md), and
+``Qwen2ForCausalLM`` (``oracle/hf_crosscheck.py``), and
 (c) golden vectors generated from this file and committed under ``tests/golden/``.
 
 What is restated, with the reference lines each piece follows
@@ -20,7 +20,7 @@ What is restated, with the reference lines each piece follows
 * prefill/decode slicing       xotorch/inference/torch/models/general_mha.py:178-254
 * sharded forward              xotorch/inference/torch/models/llm_utils.py:367-440
   (the *intended* hand-off: a non-last shard returns the OUTPUT of its last layer;
-  the reference's off-by-one, SURVEY.md 8a defect 1, is not reproduced)
+  the reference's off-by-one is not reproduced)
 * engine state machine         xotorch/inference/torch/sharded_inference_engine.py:108-193,230-370
 * sampling                     xotorch/inference/torch/sharded_inference_engine.py:208-228
 * torchtune modules (MultiHeadAttention, TransformerSelfAttentionLayer, RMSNorm,
@@ -30,7 +30,7 @@ What is restated, with the reference lines each piece follows
 Two torchtune details are kept switchable because they could not be re-read here:
 ``rmsnorm`` in {"two_round" (default, 0.6.x), "one_round"} and
 ``rope_table_dtype`` in {"bf16" (reference-exact: Module.to(bf16) casts the
-non-persistent RoPE cache, SURVEY 8a defect 3), "fp32"}.
+non-persistent RoPE cache), "fp32"}.
 """
 from __future__ import annotations
 
@@ -467,8 +467,7 @@ class OracleEngine:
 def greedy_generate(stages: List[OracleShardModel], prompt: torch.Tensor, n_new: int,
                     collect_logits: bool = False, taps_at: Tuple[int, ...] = ()):
   """Ring walk over ``stages`` (node.py:109-147,424-443) with first-index argmax
-  (equal to the product's temp=0 / top-k 35 / argmax(p/q) on every non-tied row,
-  SURVEY 8a defect 6).  Returns (tokens [B, n_new], logits list, taps list)."""
+  (equal to the product's temp=0 / top-k 35 / argmax(p/q) on every non-tied row).  Returns (tokens [B, n_new], logits list, taps list)."""
   engines = [OracleEngine(s) for s in stages]
   for e in engines:
     e.start_request(prompt)

@@ -106,7 +106,7 @@ def test_sample_reference_semantics_and_noise_stream(built_lib, tmp_path):
 
 
 def test_native_error_behaviour_and_edge_cases(built_lib):
-  """Errors raise (the reference returns None on OOM, SURVEY 8b): capacity, gaps, duplicates,
+  """Errors raise (the reference returns None on OOM): capacity, gaps, duplicates,
   exhausted page pool; slot release / reuse; page-boundary crossing."""
   from xotorch_support_jetson_b200 import model_config as mc
   from xotorch_support_jetson_b200.models import model_cards
@@ -283,7 +283,7 @@ def test_ring_last_stage_sampler_speculation_is_invisible(built_lib, tmp_path):
 
 
 def test_generate_device_loop_equals_stepwise_calls(built_lib, tmp_path):
-  """generate() (token loop on the device, SURVEY 8f.1) against the same loop driven from the host
+  """generate() (token loop on the device) against the same loop driven from the host
   call by call as Node does (node.py:109-147): same ids, same stop, same state afterwards --
   greedy and with reference-mode noise (the noise stream must be rewound past the look-ahead)."""
   from xotorch_support_jetson_b200.shard import Shard

@@ -101,7 +101,7 @@ def test_prefill_decode_parity(built_lib, mid, splits):
 
 
 def test_ragged_batch_equals_single_sequence_runs(built_lib):
-  """bs>1 has no reference execution through the API (SURVEY 8a defect 5): its oracle is
+  """bs>1 has no reference execution through the API: its oracle is
   independent bs=1 runs.  Three sequences of different lengths in one batch, sharing the
   page pool, must reproduce the per-sequence results."""
   from xotorch_support_jetson_b200.shard import Shard

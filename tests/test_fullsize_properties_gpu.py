@@ -161,7 +161,7 @@ def test_fullsize_properties(built_lib, mid, n_layers):
   assert e["prefill"] < 1.5 * worst_ref + 0.005
   assert e["decode"] < 1.5 * worst_ref + 0.005
   assert e["prefill+1"] < 1.5 * worst_ref + 0.005
-  # Stated tolerance at full size (DESIGN.md section 2): two bf16 evaluations that each sit ~0.06 of max-abs from
+  # Stated tolerance at full size: two bf16 evaluations that each sit ~0.06 of max-abs from
   # the exact answer after 28-32 layers and 2048 positions can be ~sqrt(2) x that apart from each other
   assert e["prefill vs oracle bf16"] < FULL_LOGIT_TOL and e["decode vs oracle bf16"] < FULL_LOGIT_TOL
   assert worst_h_rel < FULL_HIDDEN_TOL and worst_h_fro < FULL_HIDDEN_FRO_TOL

@@ -50,7 +50,7 @@ def test_partitioning_matches_reference_outputs():
 
 def test_reference_test_vectors_verbatim():
   """Expected values copied from the reference's test (xotorch/topology/test_map_partitions.py:9-50)
-  and from SURVEY.md 8e (8 equal nodes)."""
+  and the same strategy on 8 equal nodes."""
   from xotorch_support_jetson_b200.shard import Shard
   from xotorch_support_jetson_b200.topology import Partition, map_partitions_to_shards, pipeline_shards
   parts = [Partition("node1", 0.0, 0.42857), Partition("node2", 0.42857, 0.71428), Partition("node3", 0.71428, 0.99999)]
@@ -72,7 +72,7 @@ def test_registry_and_base_shard():
   assert models.build_base_shard("llama-3.1-8b", "TorchDynamicShardInferenceEngine") is None
   with pytest.raises(ValueError):
     get_inference_engine("mlx", None)
-  # byte counts of SURVEY.md section 8 (footnote 1)
+  # matrix bytes streamed per decode step
   for mid, gb in (("llama-3.2-1b", 2.472), ("llama-3.1-8b", 15.009), ("qwen-2.5-7b", 14.141)):
     c = models.model_cards[mid]["hf_config"]
     D, H, KV, I, V, L = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["intermediate_size"], c["vocab_size"], c["num_hidden_layers"]

@@ -2,8 +2,7 @@
 greedy tokens, CUDA engine against the oracle (the reference-equivalent CPU torch engine).
 
 Random-init logits over V = 128256 are bf16 values with frequent EXACT top-2 ties (measured
-here: the oracle's min top-2 margin over 64 steps is 0.0 for every init scale tried, SURVEY.md
-section 7 predicted 98.5 %), so "identical 64 tokens" is only well defined on a checkpoint with
+here: the oracle's min top-2 margin over 64 steps is 0.0 for every init scale tried), so "identical 64 tokens" is only well defined on a checkpoint with
 peaked logits.  Two checks:
   1. peaked checkpoint (embedding table scaled so the tied head keeps the last token dominant;
      oracle min margin ~50 bf16 ulps): 64 free-running greedy tokens must be IDENTICAL;

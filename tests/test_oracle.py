@@ -69,7 +69,7 @@ def test_sampler_restatement():
   g = torch.Generator().manual_seed(0)
   logits = torch.randn(4, 1000, generator=g) * 3
   q = torch.empty(4, 1000).exponential_(1, generator=g)
-  # temp -> 0 with top-k: argmax unless tied (SURVEY 8a defect 6)
+  # temp -> 0 with top-k: argmax unless tied
   t = O.sample(logits.clone(), temperature=0.0, top_k=35, q=q)
   assert torch.equal(t.reshape(-1).long(), logits.argmax(-1))
   # top-k pivot keeps exactly the k largest (no ties in random floats)

@@ -1,4 +1,4 @@
-"""The orchestration / networking binding (SURVEY 8 rows f3 and the Node dispatch): this package's peer
+"""The orchestration / networking binding: this package's peer
 handles, discovery, server and ``BoxNode`` against traces recorded from the reference's OWN ``Node``
 (tests/golden/ref_node_trace.json, made by oracle/gen_ref_fixtures.py with the reference's
 orchestration/node.py unmodified), and -- where /root/reference is mounted (the build container) -- against

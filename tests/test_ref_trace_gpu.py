@@ -149,7 +149,7 @@ def test_padded_prompt_equals_the_oracle_padded_branch(built_lib, tmp_path):
 
 
 def test_returned_arrays_are_owned_by_the_caller(built_lib, tmp_path):
-  """SURVEY 8b: numpy results are host-owned.  Eight requests interleaved on one engine, every
+  """numpy results are host-owned.  Eight requests interleaved on one engine, every
   result kept: none is overwritten by later calls, and once they are dropped their pinned
   buffers are reused instead of new ones being allocated."""
   from xotorch_support_jetson_b200.shard import Shard

@@ -1,6 +1,6 @@
 """ctypes binding of libxb200 (include/xb200.h).  Thin: one Python function per C entry
 point, non-zero status -> RuntimeError(xb_last_error()), exactly the error convention the
-reference's Python engine has (exceptions; SURVEY.md section 8b)."""
+reference's Python engine has (exceptions)."""
 import ctypes as C
 import os
 from pathlib import Path

@@ -2,7 +2,7 @@
 (``xotorch/inference/torch/sharded_inference_engine.py:37-424``) behind the same
 ``InferenceEngine`` methods, backed by libxb200 instead of eager torchtune modules.
 
-Differences that are deliberate ("known defects"):
+Differences that are deliberate:
 * state is keyed by ``request_id`` (one KV slot per sequence of a request) instead of a
   single mutable ``self.state`` -- concurrent requests do not corrupt each other;
 * the ``inference_state`` dict that travels between nodes holds only ``curr_pos`` and
@@ -89,7 +89,7 @@ def state_to_dict(tokens: Optional[List[List[int]]], curr_pos: int, copy: bool =
 class _PinnedPool:
   """Page-locked host buffers behind the numpy arrays the plugin API hands out.
 
-  SURVEY 8b: results are host-owned arrays the caller may keep (the reference's own contract test
+  Results are host-owned arrays the caller may keep (the reference's own contract test
   holds two results and compares them, xotorch/inference/test_inference_engine.py:43-44; a node may
   hold a hidden state while it serialises it for the next peer).  So a buffer belongs to the array
   that was returned -- and to every view derived from it -- for as long as the caller keeps it:
@@ -920,7 +920,7 @@ class B200ShardInferenceEngine(InferenceEngine):
   async def generate(self, request_id: str, shard: Shard, input_data: np.ndarray, inference_state: Optional[dict] = None, *,
                      max_generate_tokens: int = 1024, temp: float = TEMP, top_k: int = TOP_K, top_p: float = 0.0,
                      eos_token_id: Optional[int] = None, on_token=None, lookahead: int = 8) -> tuple[np.ndarray, dict]:
-    """The ring walk of a one-node ring without leaving the device (SURVEY 8f.1).
+    """The ring walk of a one-node ring without leaving the device.
 
     In the reference every generated token costs ``process_inference_result`` -> ``sample`` ->
     ``create_task(forward_tensor)`` -> ``process_tensor`` -> ``infer_tensor`` (node.py:109-147,

@@ -1,6 +1,6 @@
 // Tensor-core attention over the paged KV cache (replaces torchtune MultiHeadAttention's
 // GQA-expand + F.scaled_dot_product_attention, built at the reference's
-// xotorch/inference/torch/models/general_mha.py:78-106; SURVEY.md K5/K6).
+// xotorch/inference/torch/models/general_mha.py:78-106).
 //
 // K/V tiles of 64 keys x head_dim arrive by TMA (128B-swizzled boxes cut from the paged pool,
 // one producer warp, mbarrier full/empty ring); the math is mma.sync.m16n8k16 bf16 -> fp32

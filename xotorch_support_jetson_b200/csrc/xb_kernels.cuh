@@ -2,7 +2,7 @@
 // (split-K reduce +) residual + RMSNorm, QKV finalize (bias + RoPE + paged-KV append),
 // SiLU*up and on-device sampling (attention lives in xb_attn_mma.cuh).
 //
-// Every "rounding point" follows the reference's eager bf16 graph (SURVEY.md section 8a):
+// Every "rounding point" follows the reference's eager bf16 graph:
 // each nn.Linear output, RoPE output, attention output, residual sum, RMSNorm output,
 // SiLU output and the gate*up product are rounded to bf16 exactly once.
 #pragma once

@@ -3,7 +3,7 @@
 Same field mapping and the same quirks as the reference's ``load_model_config``
 (``xotorch/inference/torch/models/llm_utils.py:30-77``): ``rope_scaling_factor`` is read
 from the key ``"rope_factor"`` with default 32, so Llama-3.1 runs with factor 32 like the
-reference does (SURVEY.md 8a defect 2).  Family / tied-head detection by model-id
+reference does.  Family / tied-head detection by model-id
 substring follows ``general_mha.py:33-63``.
 """
 import json
@@ -179,7 +179,7 @@ def load_model_config(model_config_path: Path) -> dict:
   cfg["rope_scaling"] = scaling
   if scaling is not None:
     # reference quirk kept on purpose: the factor is looked up under "rope_factor", a key HF configs
-    # do not carry, so Llama-3.x always runs with 32 (llm_utils.py:68-69; SURVEY 8a defect 2)
+    # do not carry, so Llama-3.x always runs with 32 (llm_utils.py:68-69)
     cfg["rope_scaling_factor"] = scaling.get("rope_factor", 32)
     if os.getenv("TORCH_USE_ORG_SEQ", "False").lower() == "true":
       cfg["max_seq_len"] = scaling["original_max_position_embeddings"]
@@ -235,8 +235,8 @@ def rope_theta(family: str, config: dict) -> torch.Tensor:
 def rope_table(family: str, config: dict, n_pos: int, bf16_rounded: bool = True) -> torch.Tensor:
   """fp32 ``[n_pos, head_dim/2, 2]`` (cos, sin) table for XB_W_ROPE_TABLE.  With
   ``bf16_rounded`` the values are rounded to bf16 first: the reference's
-  ``Module.to(bfloat16)`` also casts the RoPE module's non-persistent cache
-  (SURVEY.md 8a defect 3), so this is the reference-exact table."""
+  ``Module.to(bfloat16)`` also casts the RoPE module's non-persistent cache,
+  so this is the reference-exact table."""
   theta = rope_theta(family, config)
   seq_idx = torch.arange(n_pos, dtype=theta.dtype)
   idx_theta = torch.einsum("i, j -> ij", seq_idx, theta).float()

@@ -15,7 +15,7 @@ from the partitioning strategy over the collected topology), plus what an intra-
   engine without a host copy;
 * a shard that is both first and last may keep the token loop on the device (``engine.generate``).
 
-Left out on purpose (out of scope): training entry points, stable-diffusion branch,
+Left out on purpose: training entry points, stable-diffusion branch,
 status broadcasts for the TUI, download progress, periodic re-discovery.
 """
 import asyncio

@@ -5,7 +5,7 @@ The reference's ``ShardDownloader.ensure_shard(shard, engine_name) -> Path``
 ``config.json`` + ``*.safetensors`` in HuggingFace naming.  There is no network on the
 build or GPU boxes, so ``LocalShardDownloader`` returns such a directory from local
 disk and, when asked, fills it with a seeded random-init checkpoint of the registered
-architecture (SURVEY.md section 8d: Linear/embedding N(0, std^2) in bf16, RMSNorm scales
+architecture (Linear/embedding N(0, std^2) in bf16, RMSNorm scales
 1.0 or 1+N(0, std^2), Qwen q/k/v biases N(0, std^2)).
 """
 import json
@@ -51,7 +51,7 @@ def random_hf_state(cfg: dict, seed: int = 0, std: float = 0.02, norm_jitter: fl
   """Seeded random-init state dict in HF naming.  Each tensor draws from its own
   generator (seed, name-hash) so a layer-range subset equals the same rows of the full
   model.  ``peaked_head`` > 0 plants ``lm_head = peaked_head * embed + noise`` so greedy
-  decoding has top-2 margins far above one bf16 ulp (SURVEY.md section 7, hard parts);
+  decoding has top-2 margins far above one bf16 ulp;
   ``embed_std`` scales the embedding table alone (with a tied head a larger table keeps the
   last token's own embedding visible in the residual stream, which peaks the logits)."""
   out = {}
